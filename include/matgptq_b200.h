@@ -1,0 +1,109 @@
+/*
+ * C ABI of libmatgptq_b200: the B200 (sm_100a) implementation of MatGPTQ's
+ * bit-sliced mixed-precision linear layer.
+ *
+ * Plain pointers and sizes only.  Device pointers are CUDA device addresses in the
+ * current context; `stream` is a cudaStream_t passed as void* (NULL = default
+ * stream).  Every function returns 0 on success or one of the MATGPTQ_B200_ERR_*
+ * codes; none of them calls exit() or prints.  Functions are thread-safe as long
+ * as concurrent calls do not write the same buffers.  Nothing is allocated on the
+ * device by any function in this header.
+ *
+ * Notation: N = out features, K = in features, M = activation rows (tokens),
+ * b = inference bitwidth in {2,3,4,6,8}, g = group size in {-1, 32, 128},
+ * G = K/g groups per row (1 when g = -1).
+ * Shape limits: N % 16 == 0, K % 128 == 0 (and K % g == 0).
+ */
+#ifndef MATGPTQ_B200_H
+#define MATGPTQ_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define MATGPTQ_B200_OK 0
+#define MATGPTQ_B200_ERR_BAD_ARG 1     /* bitwidth, group size, shape or null pointer */
+#define MATGPTQ_B200_ERR_CUDA 2        /* a CUDA runtime call or a kernel launch failed */
+#define MATGPTQ_B200_ERR_UNSUPPORTED 3 /* valid in the reference but not provided here */
+#define MATGPTQ_B200_ERR_ALIGNMENT 4   /* a pointer is not 16-byte aligned */
+
+/* feature flags: bits 0 and 1 are the reference's (csrc/include/common.cuh:78-86,
+ * matgptq_cuda/matgptq_linear.py:6-9); bit 2 is an addition. */
+#define MATGPTQ_B200_FLAG_ASYNC 1 /* do not synchronise the device after the launch */
+#define MATGPTQ_B200_FLAG_BF16 2  /* activations, scales and output are bfloat16 (else float16) */
+#define MATGPTQ_B200_FLAG_PDL 4   /* launch with programmatic dependent launch: weight prefetch overlaps the previous kernel */
+
+/* Library version (major*10000 + minor*100 + patch). */
+int matgptq_b200_version(void);
+
+/* Text for a status code (static storage). */
+const char *matgptq_b200_strerror(int status);
+
+/*
+ * y[M,N] = x[M,K] . Wdq^T,  Wdq[n,k] = (q[n,k] - 2^(b-1)) * s[n, k/g] * 2^(8-b),
+ * fp32 accumulation, output rounded to fp16 (or bf16 with FLAG_BF16).
+ * Replaces matmul_matgptq_host (csrc/include/gemm.h:22-32, csrc/matgptq_gemm.cu:1026-1065);
+ * argument order follows it (the reference calls N `m`, K `n` and M `k`).
+ *   w: device, packed by matgptq_b200_pack_qweights, b*N*K/32 uint32
+ *   s: device, reordered by matgptq_b200_reorder_scales, N*G 16-bit floats
+ *   x: device, [M,K] row-major, 16-byte aligned;  y: device, [M,N] row-major
+ * Any M >= 1 is accepted (the reference is only correct for M in {1,2,4} and multiples of 8).
+ */
+int matgptq_b200_matmul(int64_t bitwidth, int64_t group_size, int64_t n_out, int64_t n_in, int64_t batch,
+                        const void *w, const void *s, const void *x, void *y, void *stream, uint32_t flags);
+
+/* Same, with the launch shape forced: warps_per_cta in {1..8} row tiles per CTA and
+ * split_k in {1,2,4,8} CTAs per cluster along K (0 = choose).  For tuning and tests. */
+int matgptq_b200_matmul_tuned(int64_t bitwidth, int64_t group_size, int64_t n_out, int64_t n_in, int64_t batch,
+                              const void *w, const void *s, const void *x, void *y, void *stream, uint32_t flags,
+                              int warps_per_cta, int split_k);
+
+/*
+ * MSB slicing of 8-bit master codes to b bits with round-to-nearest and saturation.
+ * Replaces matryoshka_slice (src/quant_utils_matgpqt.py:9-17).  In and out are
+ * device buffers of numel bytes and may be the same buffer.
+ */
+int matgptq_b200_slice(const uint8_t *master_codes, uint8_t *sliced_codes, int64_t numel, int master_bitwidth,
+                       int bitwidth, void *stream);
+
+/*
+ * Pack codes[N,K] (uint8, device) into the layout the kernels read: b*N*K/32 uint32.
+ * Replaces pack_matgptq_qweights (csrc/bindings.cpp:43-84) and the CPU packers behind
+ * it (csrc/utils.cpp:22-217).  With slice_from_master == 0 the codes are already
+ * b-bit (what the reference op receives); with slice_from_master == m > 0 they are
+ * m-bit master codes and the slicing above is fused into the pack.
+ */
+int matgptq_b200_pack_qweights(const uint8_t *codes, uint32_t *packed, int64_t n_out, int64_t n_in, int bitwidth,
+                               int slice_from_master, void *stream);
+
+/* The same packing on the CPU (host pointers), and its inverse.  The reference packs
+ * on the host only (csrc/bindings.cpp:63-83); these serve hosts without a GPU and tests. */
+int matgptq_b200_pack_qweights_host(const uint8_t *codes, uint32_t *packed, int64_t n_out, int64_t n_in, int bitwidth,
+                                    int slice_from_master);
+int matgptq_b200_unpack_qweights_host(const uint32_t *packed, uint8_t *codes, int64_t n_out, int64_t n_in,
+                                      int bitwidth);
+
+/*
+ * Scales [N,G] -> [N/16, G, 16] (16-bit elements, fp16 or bf16), device or host.
+ * Replaces reorder_matgptq_scales (csrc/bindings.cpp:86-142).  In and out must differ.
+ */
+int matgptq_b200_reorder_scales(const void *scales, void *reordered, int64_t n_out, int64_t n_in, int64_t group_size,
+                                void *stream);
+int matgptq_b200_reorder_scales_host(const void *scales, void *reordered, int64_t n_out, int64_t n_in,
+                                     int64_t group_size);
+
+/*
+ * Packed weights -> dense W[N,K] in fp16/bf16, bit-exact with the reference's
+ * dequantize (src/quant_utils_matgpqt.py:19-22): W = round(s * ((code << (8-b)) - zero)).
+ * `zeros` is NULL (zero = 128, what the three-op path implies, csrc/matgptq_gemm.cu:552,631)
+ * or per-group zero points in master units, reordered like the scales.
+ */
+int matgptq_b200_dequantize(const uint32_t *packed, const void *scales, const void *zeros, void *w_out, int64_t n_out,
+                            int64_t n_in, int bitwidth, int64_t group_size, uint32_t flags, void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MATGPTQ_B200_H */

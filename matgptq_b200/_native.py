@@ -1,0 +1,68 @@
+"""ctypes binding of ``libmatgptq_b200.so`` (the C ABI in ``include/matgptq_b200.h``).
+
+There is no fallback: if the library is missing or a symbol is absent, importing the
+operators raises.  Build it with ``python -m matgptq_b200.build``.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+
+_LIB_PATH = os.path.join(os.path.dirname(os.path.abspath(__file__)), "libmatgptq_b200.so")
+
+OK = 0
+FLAG_ASYNC = 1
+FLAG_BF16 = 2
+FLAG_PDL = 4
+
+_c_i64 = ctypes.c_int64
+_c_int = ctypes.c_int
+_c_u32 = ctypes.c_uint32
+_c_ptr = ctypes.c_void_p
+
+# symbol -> (restype, argtypes); must list every function declared in include/matgptq_b200.h
+SIGNATURES = {
+    "matgptq_b200_version": (_c_int, []),
+    "matgptq_b200_strerror": (ctypes.c_char_p, [_c_int]),
+    "matgptq_b200_matmul": (_c_int, [_c_i64, _c_i64, _c_i64, _c_i64, _c_i64, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_u32]),
+    "matgptq_b200_matmul_tuned": (_c_int, [_c_i64, _c_i64, _c_i64, _c_i64, _c_i64, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_u32, _c_int, _c_int]),
+    "matgptq_b200_slice": (_c_int, [_c_ptr, _c_ptr, _c_i64, _c_int, _c_int, _c_ptr]),
+    "matgptq_b200_pack_qweights": (_c_int, [_c_ptr, _c_ptr, _c_i64, _c_i64, _c_int, _c_int, _c_ptr]),
+    "matgptq_b200_pack_qweights_host": (_c_int, [_c_ptr, _c_ptr, _c_i64, _c_i64, _c_int, _c_int]),
+    "matgptq_b200_unpack_qweights_host": (_c_int, [_c_ptr, _c_ptr, _c_i64, _c_i64, _c_int]),
+    "matgptq_b200_reorder_scales": (_c_int, [_c_ptr, _c_ptr, _c_i64, _c_i64, _c_i64, _c_ptr]),
+    "matgptq_b200_reorder_scales_host": (_c_int, [_c_ptr, _c_ptr, _c_i64, _c_i64, _c_i64]),
+    "matgptq_b200_dequantize": (_c_int, [_c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_i64, _c_i64, _c_int, _c_i64, _c_u32, _c_ptr]),
+}
+
+_lib = None
+
+
+def lib_path() -> str:
+    return _LIB_PATH
+
+
+def load() -> ctypes.CDLL:
+    """Load the shared library once and declare every signature. Raises if it is missing."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(_LIB_PATH):
+        raise ImportError(
+            f"{_LIB_PATH} not found: the CUDA library of matgptq_b200 is not built. "
+            "Run `python -m matgptq_b200.build` (needs nvcc); there is no CPU fallback."
+        )
+    lib = ctypes.CDLL(_LIB_PATH)
+    for name, (restype, argtypes) in SIGNATURES.items():
+        fn = getattr(lib, name)  # AttributeError if the symbol is not exported
+        fn.restype = restype
+        fn.argtypes = argtypes
+    _lib = lib
+    return lib
+
+
+def check(status: int, what: str) -> None:
+    """Turn a non-zero status into the RuntimeError the reference's TORCH_CHECKs raise."""
+    if status != OK:
+        msg = load().matgptq_b200_strerror(status).decode()
+        raise RuntimeError(f"{what}: {msg} (status {status})")

@@ -1,0 +1,138 @@
+// extern "C" entry points of libmatgptq_b200 (declared in include/matgptq_b200.h):
+// argument checks, then one launch.  Checks mirror csrc/bindings.cpp:50-59,88-95,
+// 153-168 of the reference; failures come back as status codes, never exit().
+#include <cuda_runtime.h>
+
+#include "../../include/matgptq_b200.h"
+#include "kernels.h"
+
+namespace {
+
+bool valid_bitwidth(int64_t b) { return b == 2 || b == 3 || b == 4 || b == 6 || b == 8; }
+bool valid_group(int64_t g) { return g == -1 || g == 32 || g == 128; }
+
+int check_shape(int64_t n_out, int64_t n_in, int64_t bitwidth, int64_t group_size) {
+  if (!valid_bitwidth(bitwidth) || !valid_group(group_size)) return MG_ERR_BAD_ARG;
+  if (n_out <= 0 || n_in <= 0 || n_out > (1 << 24) || n_in > (1 << 24)) return MG_ERR_BAD_ARG;
+  if (n_out % 16 != 0) return MG_ERR_BAD_ARG;
+  if (n_in % 64 != 0) return MG_ERR_BAD_ARG;
+  if (n_in % 128 != 0) return MG_ERR_UNSUPPORTED;  // the reference also takes K % 128 == 64
+  if (group_size != -1 && n_in % group_size != 0) return MG_ERR_BAD_ARG;
+  return MG_OK;
+}
+
+bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+}  // namespace
+
+extern "C" {
+
+int matgptq_b200_version(void) { return 100; }
+
+const char *matgptq_b200_strerror(int status) {
+  switch (status) {
+    case MG_OK: return "ok";
+    case MG_ERR_BAD_ARG: return "bad argument (bitwidth must be 2,3,4,6,8; group size -1,32,128; N % 16 == 0; K % 64 == 0; non-null pointers)";
+    case MG_ERR_CUDA: return "CUDA runtime call or kernel launch failed";
+    case MG_ERR_UNSUPPORTED: return "unsupported shape: K must be a multiple of 128";
+    case MG_ERR_ALIGNMENT: return "pointer is not 16-byte aligned";
+    default: return "unknown status";
+  }
+}
+
+int matgptq_b200_matmul_tuned(int64_t bitwidth, int64_t group_size, int64_t n_out, int64_t n_in, int64_t batch,
+                              const void *w, const void *s, const void *x, void *y, void *stream, uint32_t flags,
+                              int warps_per_cta, int split_k) {
+  const int st = check_shape(n_out, n_in, bitwidth, group_size);
+  if (st != MG_OK) return st;
+  if (batch < 0 || batch > (1 << 24)) return MG_ERR_BAD_ARG;
+  if (batch == 0) return MG_OK;
+  if (!w || !s || !x || !y) return MG_ERR_BAD_ARG;
+  if (!aligned16(w) || !aligned16(x) || (reinterpret_cast<uintptr_t>(s) & 1u) || (reinterpret_cast<uintptr_t>(y) & 1u))
+    return MG_ERR_ALIGNMENT;
+  cudaStream_t cs = static_cast<cudaStream_t>(stream);
+  const bool bf16 = (flags & MATGPTQ_B200_FLAG_BF16) != 0;
+  const bool pdl = (flags & MATGPTQ_B200_FLAG_PDL) != 0;
+  const int r = mg::gemv_launch(static_cast<int>(bitwidth), static_cast<int>(group_size), static_cast<int>(n_out),
+                                static_cast<int>(n_in), static_cast<int>(batch), w, s, x, y, bf16, pdl, warps_per_cta,
+                                split_k, cs);
+  if (r != MG_OK) return r;
+  if (!(flags & MATGPTQ_B200_FLAG_ASYNC)) {
+    // the reference synchronises the whole device in this mode (csrc/matgptq_gemm.cu:1060-1062)
+    if (cudaStreamSynchronize(cs) != cudaSuccess) return MG_ERR_CUDA;
+  }
+  return MG_OK;
+}
+
+int matgptq_b200_matmul(int64_t bitwidth, int64_t group_size, int64_t n_out, int64_t n_in, int64_t batch,
+                        const void *w, const void *s, const void *x, void *y, void *stream, uint32_t flags) {
+  return matgptq_b200_matmul_tuned(bitwidth, group_size, n_out, n_in, batch, w, s, x, y, stream, flags, 0, 0);
+}
+
+int matgptq_b200_slice(const uint8_t *master_codes, uint8_t *sliced_codes, int64_t numel, int master_bitwidth,
+                       int bitwidth, void *stream) {
+  if (!valid_bitwidth(bitwidth) || master_bitwidth < bitwidth || master_bitwidth > 8 || numel < 0) return MG_ERR_BAD_ARG;
+  if (numel == 0) return MG_OK;
+  if (!master_codes || !sliced_codes) return MG_ERR_BAD_ARG;
+  return mg::slice_launch(master_codes, sliced_codes, numel, master_bitwidth, bitwidth, static_cast<cudaStream_t>(stream));
+}
+
+int matgptq_b200_pack_qweights(const uint8_t *codes, uint32_t *packed, int64_t n_out, int64_t n_in, int bitwidth,
+                               int slice_from_master, void *stream) {
+  const int st = check_shape(n_out, n_in, bitwidth, -1);
+  if (st != MG_OK) return st;
+  if (!codes || !packed) return MG_ERR_BAD_ARG;
+  if (slice_from_master != 0 && (slice_from_master < bitwidth || slice_from_master > 8)) return MG_ERR_BAD_ARG;
+  return mg::pack_launch(codes, packed, static_cast<int>(n_out), static_cast<int>(n_in), bitwidth, slice_from_master,
+                         static_cast<cudaStream_t>(stream));
+}
+
+int matgptq_b200_pack_qweights_host(const uint8_t *codes, uint32_t *packed, int64_t n_out, int64_t n_in, int bitwidth,
+                                    int slice_from_master) {
+  const int st = check_shape(n_out, n_in, bitwidth, -1);
+  if (st != MG_OK) return st;
+  if (!codes || !packed) return MG_ERR_BAD_ARG;
+  if (slice_from_master != 0 && (slice_from_master < bitwidth || slice_from_master > 8)) return MG_ERR_BAD_ARG;
+  return mg::pack_host(codes, packed, static_cast<int>(n_out), static_cast<int>(n_in), bitwidth, slice_from_master);
+}
+
+int matgptq_b200_unpack_qweights_host(const uint32_t *packed, uint8_t *codes, int64_t n_out, int64_t n_in,
+                                      int bitwidth) {
+  const int st = check_shape(n_out, n_in, bitwidth, -1);
+  if (st != MG_OK) return st;
+  if (!codes || !packed) return MG_ERR_BAD_ARG;
+  return mg::unpack_host(packed, codes, static_cast<int>(n_out), static_cast<int>(n_in), bitwidth);
+}
+
+int matgptq_b200_reorder_scales(const void *scales, void *reordered, int64_t n_out, int64_t n_in, int64_t group_size,
+                                void *stream) {
+  const int st = check_shape(n_out, n_in, 8, group_size);
+  if (st != MG_OK) return st;
+  if (!scales || !reordered || scales == reordered) return MG_ERR_BAD_ARG;
+  return mg::reorder_scales_launch(static_cast<const uint16_t *>(scales), static_cast<uint16_t *>(reordered),
+                                   static_cast<int>(n_out), static_cast<int>(n_in), static_cast<int>(group_size),
+                                   static_cast<cudaStream_t>(stream));
+}
+
+int matgptq_b200_reorder_scales_host(const void *scales, void *reordered, int64_t n_out, int64_t n_in,
+                                     int64_t group_size) {
+  const int st = check_shape(n_out, n_in, 8, group_size);
+  if (st != MG_OK) return st;
+  if (!scales || !reordered || scales == reordered) return MG_ERR_BAD_ARG;
+  return mg::reorder_scales_host(static_cast<const uint16_t *>(scales), static_cast<uint16_t *>(reordered),
+                                 static_cast<int>(n_out), static_cast<int>(n_in), static_cast<int>(group_size));
+}
+
+int matgptq_b200_dequantize(const uint32_t *packed, const void *scales, const void *zeros, void *w_out, int64_t n_out,
+                            int64_t n_in, int bitwidth, int64_t group_size, uint32_t flags, void *stream) {
+  const int st = check_shape(n_out, n_in, bitwidth, group_size);
+  if (st != MG_OK) return st;
+  if (!packed || !scales || !w_out) return MG_ERR_BAD_ARG;
+  if (!aligned16(packed) || (reinterpret_cast<uintptr_t>(w_out) & 7u)) return MG_ERR_ALIGNMENT;
+  return mg::dequant_launch(packed, static_cast<const uint16_t *>(scales), static_cast<const uint16_t *>(zeros),
+                            static_cast<uint16_t *>(w_out), static_cast<int>(n_out), static_cast<int>(n_in), bitwidth,
+                            static_cast<int>(group_size), (flags & MATGPTQ_B200_FLAG_BF16) != 0,
+                            static_cast<cudaStream_t>(stream));
+}
+
+}  // extern "C"

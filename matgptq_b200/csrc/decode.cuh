@@ -1,0 +1,164 @@
+// In-register decode of a lane's packed words into mma A fragments.
+//
+// Replaces the reference's plane merge + magic-number converters
+// (csrc/matgptq_gemm.cu:90-295).  A pair of b-bit codes stored at bit offset p
+// of both halves of a word becomes, with ONE LOP3, the half2
+// (1024 + c_lo*2^p, 1024 + c_hi*2^p); one HFMA2 with constants (2^-p,
+// -(1024*2^-p + Z)) turns it into the exact integers (c - Z), Z = 2^(b-1).
+// Fields whose top bit would leave the 10-bit fp16 mantissa are reached through
+// one shared right shift of the word.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include "layout.cuh"
+
+namespace mg {
+
+__device__ __forceinline__ uint32_t lop3_and_or(uint32_t a, uint32_t b, uint32_t c) {
+  uint32_t r;
+  asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(r) : "r"(a), "r"(b), "r"(c));  // (a & b) | c
+  return r;
+}
+
+__device__ __forceinline__ uint32_t h2_bits(__half2 v) { return *reinterpret_cast<uint32_t *>(&v); }
+__device__ __forceinline__ __half2 bits_h2(uint32_t v) { return *reinterpret_cast<__half2 *>(&v); }
+
+constexpr uint32_t kMagic = 0x64006400u;  // half2(1024, 1024)
+
+// Bit pattern of an fp16 value that is exactly representable and normal, duplicated into both halves.
+constexpr uint32_t half2_const(float v) {
+  uint32_t sign = 0;
+  if (v < 0.0f) {
+    sign = 0x8000u;
+    v = -v;
+  }
+  int e = 0;
+  while (v >= 2.0f) {
+    v *= 0.5f;
+    ++e;
+  }
+  while (v < 1.0f) {
+    v *= 2.0f;
+    --e;
+  }
+  const uint32_t mant = static_cast<uint32_t>((v - 1.0f) * 1024.0f);
+  const uint32_t h = sign | (static_cast<uint32_t>(e + 15) << 10) | mant;
+  return h | (h << 16);
+}
+
+// (1024 + c*2^P) -> (c - Z) for both halves.
+template <int Z, int P> __device__ __forceinline__ uint32_t normalize_at(uint32_t x) {
+  constexpr float inv = 1.0f / static_cast<float>(1 << P);
+  constexpr uint32_t mul = half2_const(inv);
+  constexpr uint32_t add = half2_const(-(1024.0f * inv + static_cast<float>(Z)));
+  return h2_bits(__hfma2(bits_h2(x), bits_h2(mul), bits_h2(add)));
+}
+
+// p is a compile-time constant at every call site once the caller's loops are unrolled.
+template <int Z> __device__ __forceinline__ uint32_t normalize(uint32_t x, int p) {
+  switch (p) {
+    case 0: return normalize_at<Z, 0>(x);
+    case 2: return normalize_at<Z, 2>(x);
+    case 3: return normalize_at<Z, 3>(x);
+    case 4: return normalize_at<Z, 4>(x);
+    case 6: return normalize_at<Z, 6>(x);
+    default: return normalize_at<Z, 8>(x);
+  }
+}
+
+// Decoded pair P of a lane as half2 of exact integers (code - Z).
+template <int B> __device__ __forceinline__ uint32_t decode_pair(const uint32_t (&w)[2 * B], int P) {
+  constexpr int Z = BlockTraits<B>::ZERO;
+  if constexpr (B == 2) {
+    const int q = P & 7;
+    const uint32_t W = w[P >> 3];
+    if (q < 5) return normalize<Z>(lop3_and_or(W, 0x00030003u << (2 * q), kMagic), 2 * q);
+    return normalize<Z>(lop3_and_or(W >> 10, 0x00030003u << (2 * (q - 5)), kMagic), 2 * (q - 5));
+  } else if constexpr (B == 4) {
+    const int q = P & 3;
+    const uint32_t W = w[P >> 2];
+    if (q < 2) return normalize<Z>(lop3_and_or(W, 0x000F000Fu << (4 * q), kMagic), 4 * q);
+    return normalize<Z>(lop3_and_or(W >> 8, 0x000F000Fu << (4 * (q - 2)), kMagic), 4 * (q - 2));
+  } else if constexpr (B == 8) {
+    const uint32_t W = w[P >> 1];
+    uint32_t x;
+    if ((P & 1) == 0) {
+      x = lop3_and_or(W, 0x00FF00FFu, kMagic);
+    } else {
+      // bytes (W.b1, 0x64, W.b3, 0x64)
+      asm("prmt.b32 %0, %1, %2, 0x7351;" : "=r"(x) : "r"(W), "r"(kMagic));
+    }
+    return normalize<Z>(x, 0);
+  } else if constexpr (B == 3) {
+    const int u = P >> 4, p = P & 15;
+    if (p < 15) {
+      const int q = p % 5;
+      const uint32_t W = w[3 * u + p / 5];
+      if (q < 3) return normalize<Z>(lop3_and_or(W, 0x00070007u << (3 * q), kMagic), 3 * q);
+      return normalize<Z>(lop3_and_or(W >> 9, 0x00070007u << (3 * (q - 3)), kMagic), 3 * (q - 3));
+    }
+    uint32_t x = lop3_and_or(w[3 * u] >> 15, 0x00010001u, kMagic);
+    x = lop3_and_or(w[3 * u + 1] >> 14, 0x00020002u, x);
+    x = lop3_and_or(w[3 * u + 2] >> 13, 0x00040004u, x);
+    return normalize<Z>(x, 0);
+  } else {
+    static_assert(B == 6, "bitwidth must be one of 2, 3, 4, 6, 8");
+    const int u = P >> 3, p = P & 7;
+    if (p < 6) {
+      const uint32_t W = w[3 * u + (p >> 1)];
+      if ((p & 1) == 0) return normalize<Z>(lop3_and_or(W, 0x003F003Fu, kMagic), 0);
+      return normalize<Z>(lop3_and_or(W >> 6, 0x003F003Fu, kMagic), 0);
+    }
+    uint32_t x;
+    if (p == 6) {
+      x = lop3_and_or(w[3 * u] >> 12, 0x000F000Fu, kMagic);
+      x = lop3_and_or(w[3 * u + 1] >> 8, 0x00300030u, x);
+    } else {
+      x = lop3_and_or(w[3 * u + 1] >> 14, 0x00030003u, kMagic);
+      x = lop3_and_or(w[3 * u + 2] >> 10, 0x003C003Cu, x);
+    }
+    return normalize<Z>(x, 0);
+  }
+}
+
+// half2 of small exact integers -> bfloat162 of the same integers.
+__device__ __forceinline__ uint32_t h2_to_bf2(uint32_t v) {
+  const float2 f = __half22float2(bits_h2(v));
+  const __nv_bfloat162 r = __floats2bfloat162_rn(f.x, f.y);
+  return *reinterpret_cast<const uint32_t *>(&r);
+}
+
+// Coalesced load of a lane's words of one block (all lanes of a warp call it).
+__device__ __forceinline__ uint4 ldg_stream_v4(const void *p) {
+  uint4 r;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w)
+               : "l"(p));
+  return r;
+}
+__device__ __forceinline__ uint2 ldg_stream_v2(const void *p) {
+  uint2 r;
+  asm volatile("ld.global.nc.L1::no_allocate.v2.u32 {%0,%1}, [%2];" : "=r"(r.x), "=r"(r.y) : "l"(p));
+  return r;
+}
+
+template <int B> __device__ __forceinline__ void load_block(const uint32_t *blk, int lane, uint32_t (&w)[2 * B]) {
+  constexpr int NV = BlockTraits<B>::NV;
+  constexpr int TAIL = BlockTraits<B>::TAIL;
+#pragma unroll
+  for (int v = 0; v < NV; ++v) {
+    const uint4 q = ldg_stream_v4(blk + v * 128 + lane * 4);
+    w[4 * v + 0] = q.x;
+    w[4 * v + 1] = q.y;
+    w[4 * v + 2] = q.z;
+    w[4 * v + 3] = q.w;
+  }
+  if constexpr (TAIL == 2) {
+    const uint2 q = ldg_stream_v2(blk + NV * 128 + lane * 2);
+    w[4 * NV + 0] = q.x;
+    w[4 * NV + 1] = q.y;
+  }
+}
+
+}  // namespace mg

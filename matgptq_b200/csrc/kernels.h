@@ -1,0 +1,35 @@
+// Internal declarations shared by the translation units of libmatgptq_b200.
+#pragma once
+#include <cuda_runtime.h>
+
+#include <cstdint>
+
+// status codes returned through the C ABI (see include/matgptq_b200.h)
+#define MG_OK 0
+#define MG_ERR_BAD_ARG 1
+#define MG_ERR_CUDA 2
+#define MG_ERR_UNSUPPORTED 3
+#define MG_ERR_ALIGNMENT 4
+
+namespace mg {
+
+// gemv.cu
+void gemv_pick_config(int tiles, int kblocks, int sm_count, int *R_out, int *S_out);
+int gemv_launch(int bitwidth, int group_size, int N, int K, int M, const void *w, const void *s, const void *x,
+                void *y, bool bf16, bool pdl, int R_override, int S_override, cudaStream_t stream);
+
+// pack.cu
+int slice_launch(const uint8_t *in, uint8_t *out, long long numel, int master_bitwidth, int bitwidth,
+                 cudaStream_t stream);
+int pack_launch(const uint8_t *codes, uint32_t *packed, int N, int K, int bitwidth, int slice_from_master,
+                cudaStream_t stream);
+int pack_host(const uint8_t *codes, uint32_t *packed, int N, int K, int bitwidth, int slice_from_master);
+int unpack_host(const uint32_t *packed, uint8_t *codes, int N, int K, int bitwidth);
+int reorder_scales_launch(const uint16_t *in, uint16_t *out, int N, int K, int group_size, cudaStream_t stream);
+int reorder_scales_host(const uint16_t *in, uint16_t *out, int N, int K, int group_size);
+
+// dequant.cu
+int dequant_launch(const uint32_t *packed, const uint16_t *scales, const uint16_t *zeros, uint16_t *w_out, int N,
+                   int K, int bitwidth, int group_size, bool bf16, cudaStream_t stream);
+
+}  // namespace mg

@@ -1,0 +1,47 @@
+"""``MatGPTQLinear`` and its feature flags, as in ``inference_lib/matgptq_cuda/matgptq_linear.py:6-59``."""
+from enum import IntEnum
+
+import torch
+
+from . import ops  # noqa: F401  (registers torch.ops.matgptq_cuda.*)
+
+
+class MatGTPQ_FeatureFlags(IntEnum):
+    SYNC = 0
+    ASYNC = 1
+    IS_BF16 = 2
+    # addition: programmatic dependent launch (weight prefetch overlaps the previous kernel)
+    PDL = 4
+
+
+class MatGPTQLinear(torch.nn.Module):
+    """Linear layer over packed b-bit weights.
+
+    ``qweight``: uint8 ``[N, K]`` codes already sliced to ``bitwidth`` bits (CPU or CUDA);
+    ``scales``: ``[N, K/group_size]`` (``[N, 1]`` for ``group_size == -1``), float16 or bfloat16,
+    which also selects the activation and output dtype.
+    """
+
+    def __init__(self, qweight: torch.Tensor, scales: torch.Tensor, bitwidth: int, group_size: int):
+        super().__init__()
+        self.n_out_features: int = qweight.shape[0]
+        self.n_in_features: int = qweight.shape[1]
+        self.bitwidth: int = bitwidth
+        self.group_size: int = group_size
+
+        self.flag: int = MatGTPQ_FeatureFlags.ASYNC + MatGTPQ_FeatureFlags.IS_BF16 * (scales.dtype == torch.bfloat16)
+
+        self.matgptq_qweight = torch.nn.Parameter(
+            torch.ops.matgptq_cuda.pack_matgptq_qweights(
+                qweight, self.n_out_features, self.n_in_features, self.bitwidth, self.group_size, self.flag),
+            requires_grad=False)
+        self.matgptq_scales = torch.nn.Parameter(
+            torch.ops.matgptq_cuda.reorder_matgptq_scales(
+                scales, self.n_out_features, self.n_in_features, self.group_size),
+            requires_grad=False)
+
+    @torch.no_grad()
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        return torch.ops.matgptq_cuda.matmul_matgptq(
+            x, self.matgptq_qweight, self.matgptq_scales, self.n_out_features, self.n_in_features,
+            self.bitwidth, self.group_size, self.flag)

@@ -1,0 +1,252 @@
+"""The three operators of the reference's ``matgptq_cuda`` package, on the B200 library.
+
+Same names, schemas and argument meaning as ``inference_lib/matgptq_cuda/__init__.py:5-63``
+(Python custom ops) and ``csrc/bindings.cpp:43-191,197-207`` (checks, allocation,
+stream): ``torch.ops.matgptq_cuda.{pack_matgptq_qweights, reorder_matgptq_scales,
+matmul_matgptq}``.  PyTorch supplies device memory and the current stream; the
+work is done by ``libmatgptq_b200.so`` through its C ABI.  Two additions sit beside
+them: ``slice_pack_matgptq_qweights`` (slicing fused into packing) and
+``dequantize_matgptq`` (dense weights for checks).
+"""
+from __future__ import annotations
+
+import torch
+
+from . import _native
+
+_lib = _native.load()
+
+_BITWIDTHS = (2, 3, 4, 6, 8)
+_GROUPS = (-1, 32, 128)
+
+
+def _check_common(bitwidth: int, group_size: int, n_in_features: int) -> None:
+    # csrc/bindings.cpp:55-59
+    if bitwidth not in _BITWIDTHS:
+        raise RuntimeError("bitwidth must be one of {2, 3, 4, 6, 8}")
+    if group_size not in _GROUPS:
+        raise RuntimeError("group_size must be one of {-1, 32, 128}")
+    if group_size != -1 and n_in_features % group_size != 0:
+        raise RuntimeError(
+            f"group_size must divide n_in_features. Got group_size={group_size}, n_in_features={n_in_features}")
+
+
+def _stream_ptr(device: torch.device) -> int:
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+def _cuda_device_of(t: torch.Tensor) -> torch.device:
+    if t.is_cuda:
+        return t.device
+    if not torch.cuda.is_available():
+        raise RuntimeError("matgptq_b200 needs a CUDA device: there is no CPU implementation of this operator")
+    return torch.device("cuda", torch.cuda.current_device())
+
+
+def _pack_impl(qweights: torch.Tensor, n_out_features: int, n_in_features: int, bitwidth: int,
+               group_size: int, slice_from_master: int) -> torch.Tensor:
+    # csrc/bindings.cpp:50-59
+    if qweights.dtype != torch.uint8:
+        raise RuntimeError("qweights must be uint8")
+    if not qweights.is_contiguous():
+        raise RuntimeError("qweights must be contiguous")
+    if qweights.dim() != 2:
+        raise RuntimeError("qweights must be 2D (n_out_features, n_in_features)")
+    if qweights.size(0) != n_out_features:
+        raise RuntimeError("n_out_features does not match qweights.size(0)")
+    if qweights.size(1) != n_in_features:
+        raise RuntimeError("n_in_features does not match qweights.size(1)")
+    _check_common(bitwidth, group_size, n_in_features)
+    dev = _cuda_device_of(qweights)
+    with torch.cuda.device(dev):
+        codes = qweights.to(dev, non_blocking=True)
+        packed = torch.empty(bitwidth * n_out_features * n_in_features // 32, dtype=torch.uint32, device=dev)
+        st = _lib.matgptq_b200_pack_qweights(codes.data_ptr(), packed.data_ptr(), n_out_features, n_in_features,
+                                             bitwidth, slice_from_master, _stream_ptr(dev))
+        _native.check(st, "pack_matgptq_qweights")
+        if codes is not qweights:
+            codes.record_stream(torch.cuda.current_stream(dev))
+    return packed
+
+
+@torch.library.custom_op("matgptq_cuda::pack_matgptq_qweights", mutates_args=())
+def pack_matgptq_qweights(
+    qweights: torch.Tensor,
+    n_out_features: int,
+    n_in_features: int,
+    bitwidth: int,
+    group_size: int,
+    feature_flag: int,
+) -> torch.Tensor:
+    """Pack already-sliced b-bit codes ``[N, K]`` (uint8, CPU or CUDA) into the 1-D
+    uint32 CUDA tensor of ``b*N*K/32`` words that ``matmul_matgptq`` reads."""
+    return _pack_impl(qweights, n_out_features, n_in_features, bitwidth, group_size, 0)
+
+
+@pack_matgptq_qweights.register_fake
+def _pack_fake(qweights, n_out_features, n_in_features, bitwidth, group_size, feature_flag):
+    return qweights.new_empty((bitwidth * n_out_features * n_in_features // 32,), dtype=torch.uint32)
+
+
+@torch.library.custom_op("matgptq_cuda::slice_pack_matgptq_qweights", mutates_args=())
+def slice_pack_matgptq_qweights(
+    qweights: torch.Tensor,
+    n_out_features: int,
+    n_in_features: int,
+    master_bitwidth: int,
+    bitwidth: int,
+    group_size: int,
+    feature_flag: int,
+) -> torch.Tensor:
+    """``pack_matgptq_qweights(matryoshka_slice(qweights, master_bitwidth, bitwidth), ...)`` in one
+    pass over the master codes (the two steps of ``vllm_matgptq.py:152-166``)."""
+    if not (bitwidth <= master_bitwidth <= 8):
+        raise RuntimeError("need bitwidth <= master_bitwidth <= 8")
+    return _pack_impl(qweights, n_out_features, n_in_features, bitwidth, group_size, master_bitwidth)
+
+
+@slice_pack_matgptq_qweights.register_fake
+def _slice_pack_fake(qweights, n_out_features, n_in_features, master_bitwidth, bitwidth, group_size, feature_flag):
+    return qweights.new_empty((bitwidth * n_out_features * n_in_features // 32,), dtype=torch.uint32)
+
+
+@torch.library.custom_op("matgptq_cuda::reorder_matgptq_scales", mutates_args=())
+def reorder_matgptq_scales(scales: torch.Tensor, m: int, n: int, group_size: int) -> torch.Tensor:
+    """Reorder scales ``[N, G]`` for the kernels; same shape and dtype, on CUDA
+    (``m`` = out features, ``n`` = in features, as in the reference)."""
+    # csrc/bindings.cpp:92-97
+    if not scales.is_contiguous():
+        raise RuntimeError("scales must be contiguous")
+    if scales.dim() != 2:
+        raise RuntimeError("scales must be 2D (n_out_features, n_groups)")
+    if scales.dtype not in (torch.float16, torch.bfloat16):
+        raise RuntimeError("scales must be float16 or bfloat16")
+    _check_common(8, group_size, n)
+    groups = 1 if group_size == -1 else n // group_size
+    if scales.size(0) != m or scales.size(1) != groups:
+        raise RuntimeError(f"scales must have shape ({m}, {groups})")
+    dev = _cuda_device_of(scales)
+    with torch.cuda.device(dev):
+        src = scales.to(dev, non_blocking=True)
+        out = torch.empty_like(src)
+        st = _lib.matgptq_b200_reorder_scales(src.data_ptr(), out.data_ptr(), m, n, group_size, _stream_ptr(dev))
+        _native.check(st, "reorder_matgptq_scales")
+        if src is not scales:
+            src.record_stream(torch.cuda.current_stream(dev))
+    return out
+
+
+@reorder_matgptq_scales.register_fake
+def _reorder_fake(scales, m, n, group_size):
+    return torch.empty_like(scales)
+
+
+def _check_matmul_args(input, matgptq_weights, matgptq_scales, n_out_features, n_in_features, bitwidth, group_size):
+    # csrc/bindings.cpp:155-168
+    for name, t in (("input", input), ("matgptq_weights", matgptq_weights), ("matgptq_scales", matgptq_scales)):
+        if not t.is_cuda:
+            raise RuntimeError(f"matmul_matgptq: expected {name} to be a CUDA tensor")
+    if not (input.device == matgptq_weights.device == matgptq_scales.device):
+        raise RuntimeError("matmul_matgptq: input, matgptq_weights and matgptq_scales must be on the same GPU")
+    if matgptq_weights.dtype != torch.uint32:
+        raise RuntimeError("matgptq_weights must be uint32")
+    if not matgptq_weights.is_contiguous():
+        raise RuntimeError("matgptq_weights must be contiguous")
+    if matgptq_weights.dim() != 1:
+        raise RuntimeError("qweights must be 1D")
+    if matgptq_weights.size(0) != bitwidth * n_out_features * n_in_features // 32:
+        raise RuntimeError("matgptq_weights has the wrong size")
+    _check_common(bitwidth, group_size, n_in_features)
+    if input.dim() < 2 or input.size(-1) != n_in_features:
+        raise RuntimeError("input must have shape [..., M, n_in_features]")
+
+
+@torch.library.custom_op("matgptq_cuda::matmul_matgptq", mutates_args=())
+def matmul_matgptq(
+    input: torch.Tensor,
+    matgptq_weights: torch.Tensor,
+    matgptq_scales: torch.Tensor,
+    n_out_features: int,
+    n_in_features: int,
+    bitwidth: int,
+    group_size: int,
+    feature_flag: int,
+) -> torch.Tensor:
+    """``y[M, N] = x[M, K] @ Wdq.T`` for packed b-bit weights; ``M = input.size(-2)``.
+    Output is float16, or bfloat16 when ``feature_flag & 2``."""
+    _check_matmul_args(input, matgptq_weights, matgptq_scales, n_out_features, n_in_features, bitwidth, group_size)
+    bf16 = bool(feature_flag & _native.FLAG_BF16)
+    dtype = torch.bfloat16 if bf16 else torch.float16
+    if input.dtype != dtype or matgptq_scales.dtype != dtype:
+        raise RuntimeError(f"input and matgptq_scales must be {dtype} for feature_flag={feature_flag}")
+    dev = matgptq_weights.device
+    batch = input.size(-2)
+    x = input
+    if input.dim() > 2:
+        # the reference reads the last two dimensions only (csrc/bindings.cpp:171)
+        x = input.reshape(-1, batch, n_in_features)[0]
+    if not x.is_contiguous():
+        x = x.contiguous()
+    if x.data_ptr() % 16 != 0:
+        x = x.clone()
+    with torch.cuda.device(dev):
+        out = torch.empty((batch, n_out_features), dtype=dtype, device=dev)
+        st = _lib.matgptq_b200_matmul(bitwidth, group_size, n_out_features, n_in_features, batch,
+                                      matgptq_weights.data_ptr(), matgptq_scales.data_ptr(), x.data_ptr(),
+                                      out.data_ptr(), _stream_ptr(dev), feature_flag)
+        _native.check(st, "matmul_matgptq")
+    return out
+
+
+@matmul_matgptq.register_fake
+def _matmul_fake(input, matgptq_weights, matgptq_scales, n_out_features, n_in_features, bitwidth, group_size,
+                 feature_flag):
+    # inference_lib/matgptq_cuda/__init__.py:49-63
+    return input.new_empty((input.shape[-2], n_out_features),
+                           dtype=torch.bfloat16 if feature_flag & 2 else torch.float16)
+
+
+@torch.library.custom_op("matgptq_cuda::dequantize_matgptq", mutates_args=())
+def dequantize_matgptq(
+    matgptq_weights: torch.Tensor,
+    matgptq_scales: torch.Tensor,
+    n_out_features: int,
+    n_in_features: int,
+    bitwidth: int,
+    group_size: int,
+    feature_flag: int,
+) -> torch.Tensor:
+    """Dense ``W[N, K]`` (fp16/bf16) from packed weights and reordered scales, bit-exact with the
+    reference's ``dequantize`` for zero point 128."""
+    _check_common(bitwidth, group_size, n_in_features)
+    dev = matgptq_weights.device
+    dtype = torch.bfloat16 if feature_flag & _native.FLAG_BF16 else torch.float16
+    if matgptq_scales.dtype != dtype:
+        raise RuntimeError(f"matgptq_scales must be {dtype} for feature_flag={feature_flag}")
+    with torch.cuda.device(dev):
+        out = torch.empty((n_out_features, n_in_features), dtype=dtype, device=dev)
+        st = _lib.matgptq_b200_dequantize(matgptq_weights.data_ptr(), matgptq_scales.data_ptr(), None, out.data_ptr(),
+                                          n_out_features, n_in_features, bitwidth, group_size, feature_flag,
+                                          _stream_ptr(dev))
+        _native.check(st, "dequantize_matgptq")
+    return out
+
+
+@dequantize_matgptq.register_fake
+def _dequant_fake(matgptq_weights, matgptq_scales, n_out_features, n_in_features, bitwidth, group_size, feature_flag):
+    return matgptq_scales.new_empty((n_out_features, n_in_features))
+
+
+def matmul_matgptq_raw(x: torch.Tensor, packed: torch.Tensor, scales: torch.Tensor, n_out: int, n_in: int,
+                       bitwidth: int, group_size: int, flags: int, out: torch.Tensor | None = None,
+                       warps_per_cta: int = 0, split_k: int = 0) -> torch.Tensor:
+    """The C-ABI matmul without the dispatcher around it: no argument checks beyond the library's own,
+    optional preallocated output and forced launch shape.  Used by the decode loop and the benchmarks."""
+    batch = x.size(-2)
+    if out is None:
+        out = torch.empty((batch, n_out), dtype=x.dtype, device=x.device)
+    st = _lib.matgptq_b200_matmul_tuned(bitwidth, group_size, n_out, n_in, batch, packed.data_ptr(),
+                                        scales.data_ptr(), x.data_ptr(), out.data_ptr(),
+                                        torch.cuda.current_stream(x.device).cuda_stream, flags, warps_per_cta, split_k)
+    _native.check(st, "matgptq_b200_matmul")
+    return out
