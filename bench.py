@@ -1,0 +1,411 @@
+"""Benchmark of the bit-sliced GEMV path (and its CPU reference arm).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Workload (N = 1): the shape and bitwidth sweep of the sliced GEMV — the four Llama-3-8B
+linear shapes x batch M in {1,2,4,8,16} x inference bitwidth b in {2,3,4,6,8}, fp16, group 128,
+weights sliced from seeded 8-bit master codes.  One STEP is one pass over the 100 cells, launched
+back to back from a CUDA graph; the loop order (M, shape, b) puts 20 other weight sets (~400 MB,
+more than L2) between two uses of the same weights.  `value` is algorithmic GB/s of the whole step
+(bytes a call must move: planes + scales + activations + output).  With N > 1 the same sweep runs
+tensor-parallel: k/v and gate/up split N, q/o and down split K and all-reduce their partial outputs.
+Rank 0 prints one JSON line.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+import torch  # noqa: E402
+
+from matgptq_b200 import synth  # noqa: E402
+
+METRIC = "sliced_gemv_algorithmic_bandwidth"
+UNIT = "GB/s"
+BATCHES = (1, 2, 4, 8, 16)
+BITS = synth.BITWIDTHS
+GROUP = 128
+ROW_PARALLEL = {"q_o": True, "k_v": False, "gate_up": False, "down": True}
+
+
+def measured_peaks() -> tuple[float, str]:
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index = index
+        self.samples: list[list[str]] = []
+        self.proc = None
+        self.thread = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+            return
+        self.thread = threading.Thread(target=self._read, daemon=True)
+        self.thread.start()
+
+    def _read(self):
+        for line in self.proc.stdout:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) == 6:
+                self.samples.append(parts)
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        clocks, reasons, maxc = [], set(), None
+        for s in self.samples:
+            try:
+                clocks.append(float(s[0]))
+                maxc = float(s[1])
+            except ValueError:
+                continue
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), s[2:]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(clocks) if clocks else None, "sm_max_mhz": maxc,
+                "reasons": sorted(reasons), "samples": len(clocks)}
+
+
+# --------------------------------------------------------------------------------------
+# reference arm / CPU baseline: the oracle's dequantise-then-matmul on the host cores
+# --------------------------------------------------------------------------------------
+def cpu_sample_cells():
+    """Bounded sample of the sweep for the CPU arm: M = 1, q/o shape, every bitwidth."""
+    k, n = synth.LLAMA3_8B_SHAPES["q_o"]
+    return [("q_o", k, n, 1, b) for b in BITS]
+
+
+def run_cpu_arm(steps: int, warmup: int) -> dict:
+    from oracle import matgptq_oracle as oracle
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    cells = cpu_sample_cells()
+    layer = synth.make_layer(4096, 4096, GROUP, seed=1, sym=True, dtype=torch.float16)
+    x = synth.make_activations(1, 4096, seed=1, dtype=torch.float16)
+    nbytes = sum(synth.algorithmic_bytes(n, k, m, b, GROUP) for _, k, n, m, b in cells)
+
+    def step():
+        for _, k, n, m, b in cells:
+            oracle.fake_matryoshka_linear(x, layer.qweight, layer.scales, layer.zeros, 8, b)
+
+    for _ in range(warmup):
+        step()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        step()
+    dt = (time.perf_counter() - t0) / steps
+    return {"value": nbytes / dt / 1e9, "ms_per_step": dt * 1e3, "cores": cores,
+            "sample": "oracle dequantise-then-matmul (torch CPU, fp16), 4096x4096, M=1, b in {2,3,4,6,8}: 5 cells per step"}
+
+
+def reference_main(args) -> None:
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    r = run_cpu_arm(args.steps, args.warmup)
+    line = {
+        "impl": "reference", "metric": METRIC, "value": r["value"], "unit": UNIT, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": r["ms_per_step"], "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+        "config": {"workload": "llama3-8b linear shapes x M{1,2,4,8,16} x b{2,3,4,6,8}, g128, fp16 (bounded CPU sample)"},
+        "cpu_baseline": {"value": r["value"], "unit": UNIT, "cores": r["cores"], "kind": "port", "sample": r["sample"]},
+        "e2e": {"value": r["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# --------------------------------------------------------------------------------------
+# our arm
+# --------------------------------------------------------------------------------------
+def build_cells(world: int, rank: int, dev: torch.device):
+    """Pack this rank's shard of every (shape, b) and allocate activations/outputs for every M."""
+    from matgptq_b200 import ops  # noqa: F401
+    weights = {}
+    for si, (name, (k, n)) in enumerate(synth.LLAMA3_8B_SHAPES.items()):
+        if world > 1 and ROW_PARALLEL[name]:
+            k_loc, n_loc = k // world, n
+        elif world > 1:
+            k_loc, n_loc = k, n // world
+        else:
+            k_loc, n_loc = k, n
+        layer = synth.make_layer(n_loc, k_loc, GROUP, seed=100 * si + rank, sym=True, dtype=torch.float16, device=dev)
+        scales_r = torch.ops.matgptq_cuda.reorder_matgptq_scales(layer.scales, n_loc, k_loc, GROUP)
+        for b in BITS:
+            packed = torch.ops.matgptq_cuda.slice_pack_matgptq_qweights(layer.qweight, n_loc, k_loc, 8, b, GROUP, 1)
+            weights[(name, b)] = (packed, scales_r, n_loc, k_loc)
+        del layer
+    cells = []
+    for m in BATCHES:
+        for name, (k, n) in synth.LLAMA3_8B_SHAPES.items():
+            for b in BITS:
+                packed, scales_r, n_loc, k_loc = weights[(name, b)]
+                x = synth.make_activations(m, k_loc, seed=m, dtype=torch.float16, device=dev)
+                y = torch.empty(m, n_loc, dtype=torch.float16, device=dev)
+                cells.append({"name": name, "m": m, "b": b, "k": k, "n": n, "k_loc": k_loc, "n_loc": n_loc,
+                              "packed": packed, "scales": scales_r, "x": x, "y": y,
+                              "bytes": synth.algorithmic_bytes(n, k, m, b, GROUP)})
+    return cells
+
+
+def launch_cell(c, flags: int, world: int):
+    from matgptq_b200 import ops
+    ops.matmul_matgptq_raw(c["x"], c["packed"], c["scales"], c["n_loc"], c["k_loc"], c["b"], GROUP, flags, out=c["y"])
+    if world > 1 and ROW_PARALLEL[c["name"]]:
+        torch.distributed.all_reduce(c["y"])
+
+
+def per_cell_table(dev: torch.device, flags: int) -> dict:
+    """Cold-L2 time of every cell on its own: a graph of launches cycling over enough copies of the
+    cell's weights to exceed L2 several times over. Returns per-bitwidth and per-cell figures."""
+    from matgptq_b200 import ops
+    out_cells = []
+    for si, (name, (k, n)) in enumerate(synth.LLAMA3_8B_SHAPES.items()):
+        layer = synth.make_layer(n, k, GROUP, seed=100 * si, sym=True, dtype=torch.float16, device=dev)
+        scales_r = torch.ops.matgptq_cuda.reorder_matgptq_scales(layer.scales, n, k, GROUP)
+        for b in BITS:
+            packed = torch.ops.matgptq_cuda.slice_pack_matgptq_qweights(layer.qweight, n, k, 8, b, GROUP, 1)
+            wbytes = packed.numel() * 4
+            copies = max(2, min(64, -(-512 * 1024 * 1024 // wbytes)))
+            packs = [packed] + [packed.clone() for _ in range(copies - 1)]
+            scs = [scales_r] + [scales_r.clone() for _ in range(copies - 1)]
+            for m in BATCHES:
+                x = synth.make_activations(m, k, seed=m, dtype=torch.float16, device=dev)
+                y = torch.empty(m, n, dtype=torch.float16, device=dev)
+                reps = copies * 2
+                stream = torch.cuda.Stream(device=dev)
+                with torch.cuda.stream(stream):
+                    for i in range(copies):
+                        ops.matmul_matgptq_raw(x, packs[i], scs[i], n, k, b, GROUP, flags, out=y)
+                    stream.synchronize()
+                    graph = torch.cuda.CUDAGraph()
+                    with torch.cuda.graph(graph, stream=stream):
+                        for i in range(reps):
+                            ops.matmul_matgptq_raw(x, packs[i % copies], scs[i % copies], n, k, b, GROUP, flags, out=y)
+                    graph.replay()
+                    stream.synchronize()
+                    times = []
+                    for _ in range(5):
+                        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                        e0.record(stream)
+                        graph.replay()
+                        e1.record(stream)
+                        stream.synchronize()
+                        times.append(e0.elapsed_time(e1) * 1e3 / reps)
+                us = statistics.median(times)
+                nbytes = synth.algorithmic_bytes(n, k, m, b, GROUP)
+                out_cells.append({"shape": name, "k": k, "n": n, "m": m, "b": b, "us": round(us, 3),
+                                  "gbs": round(nbytes / us / 1e3, 1)})
+                del graph
+            del packs, scs, packed
+        del layer
+    per_b = {}
+    for b in BITS:
+        sel = [c for c in out_cells if c["b"] == b]
+        tot_us = sum(c["us"] for c in sel)
+        tot_bytes = sum(synth.algorithmic_bytes(c["n"], c["k"], c["m"], b, GROUP) for c in sel)
+        per_b[str(b)] = {"mean_us": round(tot_us / len(sel), 3), "gbs": round(tot_bytes / tot_us / 1e3, 1)}
+    return {"per_bitwidth": per_b, "cells": out_cells}
+
+
+def ours_main(args) -> None:
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    assert torch.cuda.is_available(), "bench.py needs a CUDA device (there is no CPU path)"
+    dev = torch.device("cuda", local_rank)
+    torch.cuda.set_device(dev)
+    if world > 1:
+        torch.distributed.init_process_group("nccl", device_id=dev)
+    from matgptq_b200 import _native, ops  # noqa: F401
+
+    flags = _native.FLAG_ASYNC | (_native.FLAG_PDL if not args.no_pdl else 0)
+    cells = build_cells(world, rank, dev)
+    step_bytes = sum(c["bytes"] for c in cells)
+    launches_per_step = len(cells)
+
+    stream = torch.cuda.Stream(device=dev)
+    with torch.cuda.stream(stream):
+        for c in cells:  # eager pass: loads kernels, NCCL channels
+            launch_cell(c, flags, world)
+        stream.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            for c in cells:
+                launch_cell(c, flags, world)
+        for _ in range(max(args.warmup, 3)):
+            graph.replay()
+        stream.synchronize()
+        if world > 1:
+            torch.distributed.barrier()
+        torch.cuda.synchronize()
+        sampler = ClockSampler(local_rank)
+        if rank == 0:
+            sampler.start()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for _ in range(args.steps):
+            graph.replay()
+        e1.record(stream)
+        stream.synchronize()
+        torch.cuda.synchronize()
+        if world > 1:
+            torch.distributed.barrier()
+        elapsed_ms = e0.elapsed_time(e1)
+        clocks = sampler.stop() if rank == 0 else None
+    if world > 1:
+        t = torch.tensor([elapsed_ms], device=dev, dtype=torch.float64)
+        torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
+        elapsed_ms = float(t.item())
+    ms_per_step = elapsed_ms / args.steps
+    value = step_bytes / (ms_per_step * 1e-3) / 1e9
+
+    # end to end through the operator, host buffers in, host buffers out
+    e2e = None
+    if world == 1:
+        e2e = run_e2e(cells, dev, flags, max(1, min(args.steps, 5)))
+
+    extra = {}
+    cpu = None
+    if rank == 0 and world == 1:
+        if not args.no_table:
+            extra = per_cell_table(dev, flags)
+        cpu = run_cpu_arm(steps=2, warmup=1)
+
+    if rank != 0:
+        if world > 1:
+            torch.distributed.destroy_process_group()
+        return
+    peak, peak_kind = measured_peaks()
+    line = {
+        "metric": METRIC, "value": round(value, 2), "unit": UNIT, "n_gpus": world, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": round(ms_per_step, 5), "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+        "config": {"workload": "llama3-8b linear shapes (q/o 4096x4096, k/v 4096x1024, gate/up 4096x14336, down 14336x4096) "
+                               "x M{1,2,4,8,16} x b{2,3,4,6,8}, g128, fp16, sliced from 8-bit masters",
+                   "cells_per_step": launches_per_step, "l2_policy": "inputs larger than L2: ~400 MB of other weights between reuses",
+                   "parallelism": "tp%d" % world if world > 1 else "single", "pdl": not args.no_pdl},
+        "clocks": clocks,
+        "gpu_launches": launches_per_step * args.steps,
+        "roofline": {"bound": "hbm", "achieved": round(value / world, 2), "peak": peak, "unit": "GB/s",
+                     "frac": round(value / world / peak, 4), "traffic": None, "peak_kind": peak_kind,
+                     "kernel": "mg::gemv_kernel (all instantiations of the step)",
+                     "bytes_per_step": step_bytes},
+    }
+    if e2e is not None:
+        line["e2e"] = e2e
+    if cpu is not None:
+        line["cpu_baseline"] = {"value": round(cpu["value"], 4), "unit": UNIT, "cores": cpu["cores"], "kind": "port",
+                                "sample": cpu["sample"]}
+    line.update(extra)
+    print(json.dumps(line), flush=True)
+    if world > 1:
+        torch.distributed.destroy_process_group()
+
+
+def run_e2e(cells, dev, flags, steps: int) -> dict:
+    """The same step through torch.ops.matgptq_cuda.matmul_matgptq with pinned host activations in and
+    host outputs out: per cell one H2D copy, one operator call, one D2H copy."""
+    host_x = [c["x"].cpu().pin_memory() for c in cells]
+    host_y = [torch.empty(c["m"], c["n"], dtype=torch.float16).pin_memory() for c in cells]
+    h2d = sum(x.numel() * 2 for x in host_x)
+    d2h = sum(y.numel() * 2 for y in host_y)
+    step_bytes = sum(c["bytes"] for c in cells)
+    op = torch.ops.matgptq_cuda.matmul_matgptq
+
+    def step():
+        for c, hx, hy in zip(cells, host_x, host_y):
+            xd = hx.to(dev, non_blocking=True)
+            y = op(xd, c["packed"], c["scales"], c["n_loc"], c["k_loc"], c["b"], GROUP, flags)
+            hy.copy_(y, non_blocking=True)
+
+    for _ in range(2):
+        step()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        step()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / steps
+    return {"value": round(step_bytes / (ms * 1e-3) / 1e9, 2), "unit": UNIT, "ms_per_step": round(ms, 4),
+            "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h}
+
+
+def single_cell_main(args) -> None:
+    """Launch one cell a few times, eagerly, over rotating weight copies (for profilers)."""
+    from matgptq_b200 import _native, ops
+    name, b, m = args.cell.split(":")
+    b, m = int(b), int(m)
+    k, n = synth.LLAMA3_8B_SHAPES[name]
+    dev = torch.device("cuda", 0)
+    layer = synth.make_layer(n, k, GROUP, seed=1, sym=True, dtype=torch.float16, device=dev)
+    scales_r = torch.ops.matgptq_cuda.reorder_matgptq_scales(layer.scales, n, k, GROUP)
+    packed = torch.ops.matgptq_cuda.slice_pack_matgptq_qweights(layer.qweight, n, k, 8, b, GROUP, 1)
+    copies = max(2, min(32, -(-256 * 1024 * 1024 // (packed.numel() * 4))))
+    packs = [packed] + [packed.clone() for _ in range(copies - 1)]
+    x = synth.make_activations(m, k, seed=m, dtype=torch.float16, device=dev)
+    y = torch.empty(m, n, dtype=torch.float16, device=dev)
+    flags = _native.FLAG_ASYNC | (_native.FLAG_PDL if not args.no_pdl else 0)
+    torch.cuda.synchronize()
+    for i in range(args.launches):
+        ops.matmul_matgptq_raw(x, packs[i % copies], scales_r, n, k, b, GROUP, flags, out=y)
+    torch.cuda.synchronize()
+    print(json.dumps({"cell": args.cell, "launches": args.launches, "copies": copies,
+                      "algorithmic_bytes": synth.algorithmic_bytes(n, k, m, b, GROUP)}))
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--cell", type=str, default=None,
+                    help="shape:b:m, e.g. q_o:4:1 - only launch this cell (--launches times) and exit")
+    ap.add_argument("--launches", type=int, default=8)
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    ap.add_argument("--no-pdl", action="store_true", help="launch without programmatic dependent launch")
+    ap.add_argument("--no-table", action="store_true", help="skip the per-cell cold-L2 table")
+    args = ap.parse_args()
+    if args.cell:
+        single_cell_main(args)
+    elif args.impl == "reference":
+        reference_main(args)
+    else:
+        ours_main(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -103,6 +103,16 @@ int matgptq_b200_reorder_scales_host(const void *scales, void *reordered, int64_
 int matgptq_b200_dequantize(const uint32_t *packed, const void *scales, const void *zeros, void *w_out, int64_t n_out,
                             int64_t n_in, int bitwidth, int64_t group_size, uint32_t flags, void *stream);
 
+/*
+ * Waits inside the kernels (on asynchronous copies) are bounded: a kernel that gives
+ * up records a non-zero code instead of hanging, and its output is then undefined.
+ * This call synchronises with the device, returns the first code recorded on the
+ * current device since the last reset (0 = none; 101 weight copy, 102 activation
+ * copy, 103 tensor-core completion) and clears it when reset != 0.  The reference has
+ * no counterpart: its only error path is exit(1) in CHECK_CUDA (csrc/include/common.cuh:44-51).
+ */
+int matgptq_b200_device_status(int *status_out, int reset);
+
 #ifdef __cplusplus
 }
 #endif

@@ -32,6 +32,7 @@ SIGNATURES = {
     "matgptq_b200_unpack_qweights_host": (_c_int, [_c_ptr, _c_ptr, _c_i64, _c_i64, _c_int]),
     "matgptq_b200_reorder_scales": (_c_int, [_c_ptr, _c_ptr, _c_i64, _c_i64, _c_i64, _c_ptr]),
     "matgptq_b200_reorder_scales_host": (_c_int, [_c_ptr, _c_ptr, _c_i64, _c_i64, _c_i64]),
+    "matgptq_b200_device_status": (_c_int, [ctypes.POINTER(ctypes.c_int), _c_int]),
     "matgptq_b200_dequantize": (_c_int, [_c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_i64, _c_i64, _c_int, _c_i64, _c_u32, _c_ptr]),
 }
 
@@ -59,6 +60,13 @@ def load() -> ctypes.CDLL:
         fn.argtypes = argtypes
     _lib = lib
     return lib
+
+
+def device_status(reset: bool = True) -> int:
+    """First failure code recorded by a kernel on the current device (0 = none); synchronises."""
+    out = ctypes.c_int(0)
+    check(load().matgptq_b200_device_status(ctypes.byref(out), 1 if reset else 0), "device_status")
+    return out.value
 
 
 def check(status: int, what: str) -> None:

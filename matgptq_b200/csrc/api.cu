@@ -48,7 +48,7 @@ int matgptq_b200_matmul_tuned(int64_t bitwidth, int64_t group_size, int64_t n_ou
   if (batch < 0 || batch > (1 << 24)) return MG_ERR_BAD_ARG;
   if (batch == 0) return MG_OK;
   if (!w || !s || !x || !y) return MG_ERR_BAD_ARG;
-  if (!aligned16(w) || !aligned16(x) || (reinterpret_cast<uintptr_t>(s) & 1u) || (reinterpret_cast<uintptr_t>(y) & 1u))
+  if (!aligned16(w) || !aligned16(x) || !aligned16(s) || (reinterpret_cast<uintptr_t>(y) & 1u))
     return MG_ERR_ALIGNMENT;
   cudaStream_t cs = static_cast<cudaStream_t>(stream);
   const bool bf16 = (flags & MATGPTQ_B200_FLAG_BF16) != 0;
@@ -133,6 +133,11 @@ int matgptq_b200_dequantize(const uint32_t *packed, const void *scales, const vo
                             static_cast<uint16_t *>(w_out), static_cast<int>(n_out), static_cast<int>(n_in), bitwidth,
                             static_cast<int>(group_size), (flags & MATGPTQ_B200_FLAG_BF16) != 0,
                             static_cast<cudaStream_t>(stream));
+}
+
+int matgptq_b200_device_status(int *status_out, int reset) {
+  if (cudaDeviceSynchronize() != cudaSuccess) return MG_ERR_CUDA;
+  return mg::gemv_device_status(status_out, reset);
 }
 
 }  // extern "C"

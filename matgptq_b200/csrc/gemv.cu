@@ -5,24 +5,31 @@
 // Wdq[n,k] = (q[n,k] - 2^(b-1)) * s[n, k/g] * 2^(8-b), fp32 accumulation.
 //
 // Shape of the computation
-//   * one warp streams 16 out-features x a K slice: per block (16 x 128 codes) it
-//     issues 16-byte coalesced loads, decodes its 64 codes in registers straight
-//     into mma.m16n8k16 A fragments (exact integers), multiplies them with the
-//     activation fragments on the tensor pipe into a per-group fp32 accumulator
-//     and folds the group's scale in fp32 (one FMA per accumulator and group);
+//   * one warp streams 16 out-features x a K slice.  Lane 0 moves the slice with
+//     bulk asynchronous copies (cp.async.bulk, the untiled TMA path) into a ring of
+//     shared-memory stages guarded by mbarriers, a few KB ahead of the math, so the
+//     bytes in flight do not depend on registers or occupancy;
+//   * per block (16 x 128 codes) a lane reads its words with 16-byte shared loads,
+//     decodes its 64 codes in registers straight into mma.m16n8k16 A fragments
+//     (exact integers), multiplies them with the activation fragments on the
+//     tensor pipe into a per-group fp32 accumulator and folds the group's scale in
+//     fp32 (one FMA per accumulator and group);
 //   * the R warps of a CTA cover R consecutive row tiles over the same K slice and
 //     share the activation slice staged once in shared memory;
 //   * K is split over the S CTAs of a thread-block cluster (split-K for skinny
 //     shapes); partial sums meet in distributed shared memory and are added in a
 //     fixed order, so results do not depend on scheduling and no global scratch
 //     or atomics are used;
-//   * weight loads of the first blocks are issued before griddepcontrol.wait, so
-//     with programmatic dependent launch they overlap the previous kernel's tail.
+//   * the weight copies of the first stages are issued before griddepcontrol.wait,
+//     so with programmatic dependent launch they overlap the previous kernel's tail;
+//   * every mbarrier wait is bounded (async.cuh): on a timeout the kernel records a
+//     status word and finishes.
 #include <cooperative_groups.h>
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 
+#include "async.cuh"
 #include "decode.cuh"
 #include "kernels.h"
 
@@ -78,32 +85,44 @@ __device__ __forceinline__ uint16_t ldg_u16(const uint16_t *p) {
   return r;
 }
 
-// Scales a lane needs for one block: rows g and g+8 of each group in the block.
-template <int GS> struct ScaleRegs {
-  static constexpr int NG = (GS == 32) ? 4 : 1;
-  uint16_t lo[NG], hi[NG];
+// Blocks per ring stage: about 2 KB of packed weights.
+template <int B> struct ChunkBlocks {
+  static constexpr int value = (B == 2) ? 4 : (B == 3 || B == 4) ? 2 : 1;
+};
+constexpr int kStages = 4;   // ring stages per warp
+// blocks (128 in-features each) per activation stage: a multiple of every ChunkBlocks value
+template <int NT> struct XBlocks {
+  static constexpr int value = (NT == 1) ? 8 : 4;
 };
 
-template <int GS>
-__device__ __forceinline__ void load_scales(const uint16_t *s, int tile, int kb, int groups, int lane, ScaleRegs<GS> &r) {
-  if constexpr (GS == -1) {
-    (void)s; (void)tile; (void)kb; (void)groups; (void)lane; (void)r;
-  } else {
-    constexpr int NG = ScaleRegs<GS>::NG;
-    const uint16_t *base = s + (static_cast<size_t>(tile) * groups + static_cast<size_t>(kb) * NG) * 16 + (lane >> 2);
-#pragma unroll
-    for (int j = 0; j < NG; ++j) {
-      r.lo[j] = ldg_u16(base + j * 16);
-      r.hi[j] = ldg_u16(base + j * 16 + 8);
-    }
-  }
+// Shared-memory plan of one CTA, computed identically on host and device.
+struct SmemPlan {
+  int xrows, xstride_h, rstride, stage_bytes, scale_bytes_per_block;
+  int off_bars, off_x, off_red, off_ring, total;
+};
+
+template <int B, int GS, int NT>
+__host__ __device__ inline SmemPlan make_plan(int R, int M, int max_nblk) {
+  SmemPlan p;
+  p.xrows = M < NT * 8 ? M : NT * 8;
+  const int xb = max_nblk < XBlocks<NT>::value ? max_nblk : XBlocks<NT>::value;
+  p.xstride_h = xb * 128 + 32;  // halves; +64 bytes keeps 16-byte fragment reads conflict free
+  p.rstride = R * 16 + 4;
+  p.scale_bytes_per_block = (GS == -1) ? 0 : (GS == 32 ? 128 : 32);
+  p.stage_bytes = ChunkBlocks<B>::value * (BlockTraits<B>::WORDS * 4 + p.scale_bytes_per_block);
+  p.off_bars = 0;
+  p.off_x = 128 * ((8 * (R * kStages + 2) + 127) / 128);
+  p.off_red = p.off_x + 2 * p.xrows * p.xstride_h * 2;
+  p.off_ring = 128 * ((p.off_red + NT * 8 * p.rstride * 4 + 127) / 128);
+  p.total = p.off_ring + R * kStages * p.stage_bytes;
+  return p;
 }
 
 // B: bitwidth, GS: group size (-1, 32, 128), BF16: activation/scale/output type,
-// NT: batch tiles of 8 rows handled per pass, D: blocks a warp keeps in flight.
-template <int B, int GS, bool BF16, int NT, int D>
+// NT: batch tiles of 8 rows handled per pass.
+template <int B, int GS, bool BF16, int NT>
 __global__ void __launch_bounds__(256) gemv_kernel(const GemvParams p) {
-  extern __shared__ __align__(16) unsigned char smem_raw[];
+  extern __shared__ __align__(128) unsigned char smem_raw[];
 
   const int lane = threadIdx.x & 31;
   const int warp = threadIdx.x >> 5;
@@ -122,25 +141,47 @@ __global__ void __launch_bounds__(256) gemv_kernel(const GemvParams p) {
   const int mvalid = min(p.M - m0, NT * 8);
   const int groups = (GS == -1) ? 1 : p.K / GS;
 
-  // shared memory: activation stage [NT*8][stage + 32 halves], then partial sums [NT*8][R*16 + 4] floats
-  constexpr int XB = D * ((16 + D - 1) / D);  // blocks per activation stage, a multiple of D
-  const int stage_blocks = min(max_nblk, XB);
-  const int xstride = stage_blocks * 128 + 32;  // halves; +64 bytes keeps 16-byte fragment reads conflict free
-  uint16_t *xs = reinterpret_cast<uint16_t *>(smem_raw);
-  const int rstride = R * 16 + 4;
-  float *red = reinterpret_cast<float *>(smem_raw + static_cast<size_t>(NT * 8) * xstride * 2);
-
+  constexpr int CB = ChunkBlocks<B>::value;
+  constexpr int kXBlocks = XBlocks<NT>::value;
   constexpr int BW = BlockTraits<B>::WORDS;
-  const uint32_t *wbase = p.w + (static_cast<size_t>(active ? tile : 0) * p.kblocks + kb_lo) * BW;
+  constexpr int WBYTES = BW * 4;  // packed bytes per block
+  const SmemPlan plan = make_plan<B, GS, NT>(R, p.M, max_nblk);
+  const uint32_t smem_base = smem_u32(smem_raw);
+  const uint32_t bar_full0 = smem_base + plan.off_bars + warp * kStages * 8;  // this warp's ring barriers
+  const uint32_t bar_x0 = smem_base + plan.off_bars + R * kStages * 8;        // two activation barriers
+  const uint16_t *xs = reinterpret_cast<const uint16_t *>(smem_raw + plan.off_x);
+  float *red = reinterpret_cast<float *>(smem_raw + plan.off_red);
+  const unsigned char *ring = smem_raw + plan.off_ring + warp * kStages * plan.stage_bytes;
+  const uint32_t ring_u32 = smem_base + plan.off_ring + warp * kStages * plan.stage_bytes;
+  const int xstride = plan.xstride_h;
+  const int rstride = plan.rstride;
+  const int SCB = plan.scale_bytes_per_block;
 
-  uint32_t wbuf[D][2 * B];
-  ScaleRegs<GS> sbuf[D];
-#pragma unroll
-  for (int d = 0; d < D; ++d) {
-    if (active && d < nblk) {
-      load_block<B>(wbase + static_cast<size_t>(d) * BW, lane, wbuf[d]);
-      load_scales<GS>(p.s, tile, kb_lo + d, groups, lane, sbuf[d]);
-    }
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < R * kStages + 2; ++i) mbar_init(smem_base + plan.off_bars + i * 8, 1);
+    mbar_init_fence();
+  }
+  __syncthreads();
+
+  const int nchunks = (nblk + CB - 1) / CB;
+  const unsigned char *wsrc = reinterpret_cast<const unsigned char *>(p.w) +
+                              (static_cast<size_t>(active ? tile : 0) * p.kblocks + kb_lo) * WBYTES;
+  const unsigned char *ssrc = reinterpret_cast<const unsigned char *>(p.s) +
+                              (static_cast<size_t>(active ? tile : 0) * groups) * 32 + static_cast<size_t>(kb_lo) * SCB;
+
+  // lane 0: fill ring stage (c % kStages) with chunk c (weights, then the scales of its blocks)
+  auto issue_chunk = [&](int c) {
+    const int nb = min(CB, nblk - c * CB);
+    const int st = c % kStages;
+    const uint32_t bar = bar_full0 + st * 8;
+    const uint32_t dst = ring_u32 + st * plan.stage_bytes;
+    mbar_arrive_expect_tx(bar, nb * (WBYTES + SCB));
+    bulk_copy_g2s(dst, wsrc + static_cast<size_t>(c) * CB * WBYTES, nb * WBYTES, bar);
+    if (GS != -1) bulk_copy_g2s(dst + CB * WBYTES, ssrc + static_cast<size_t>(c) * CB * SCB, nb * SCB, bar);
+  };
+
+  if (active && lane == 0) {
+    for (int c = 0; c < kStages && c < nchunks; ++c) issue_chunk(c);
   }
 
   // Everything above reads only weights and scales, which no kernel writes.  The
@@ -148,94 +189,147 @@ __global__ void __launch_bounds__(256) gemv_kernel(const GemvParams p) {
   asm volatile("griddepcontrol.launch_dependents;");
   asm volatile("griddepcontrol.wait;" ::: "memory");
 
+  const int nxst = (nblk + kXBlocks - 1) / kXBlocks;
+  // thread 0: copy the activations of x stage xi (rows m0.., blocks [xi*kXBlocks, ...)) into buffer xi & 1
+  auto issue_x = [&](int xi) {
+    const int nb = min(kXBlocks, nblk - xi * kXBlocks);
+    const uint32_t bar = bar_x0 + (xi & 1) * 8;
+    const uint32_t dst = smem_base + plan.off_x + (xi & 1) * plan.xrows * xstride * 2;
+    mbar_arrive_expect_tx(bar, mvalid * nb * 256);
+    const uint16_t *src = p.x + static_cast<size_t>(m0) * p.K + static_cast<size_t>(kb_lo + xi * kXBlocks) * 128;
+    for (int m = 0; m < mvalid; ++m) bulk_copy_g2s(dst + m * xstride * 2, src + static_cast<size_t>(m) * p.K, nb * 256, bar);
+  };
+  if (threadIdx.x == 0) {
+    issue_x(0);
+    if (nxst > 1) issue_x(1);
+  }
+
   float yacc[NT][4];
 #pragma unroll
   for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
     for (int e = 0; e < 4; ++e) yacc[nt][e] = 0.f;
 
-  for (int st = 0; st < nblk; st += XB) {
-    // stage the activations of blocks [st, st + XB) of this CTA's K slice
-    const int st_blocks = min(XB, nblk - st);
-    if (st > 0) __syncthreads();
-    {
-      const int chunks = st_blocks * 16;  // 16-byte chunks per activation row in this stage
-      const uint16_t *xsrc = p.x + static_cast<size_t>(m0) * p.K + static_cast<size_t>(kb_lo + st) * 128;
-      for (int idx = threadIdx.x; idx < mvalid * chunks; idx += blockDim.x) {
-        const int m = idx / chunks, c = idx - m * chunks;
-        const uint4 v = *reinterpret_cast<const uint4 *>(xsrc + static_cast<size_t>(m) * p.K + c * 8);
-        *reinterpret_cast<uint4 *>(xs + m * xstride + c * 8) = v;
-      }
+  bool failed = false;
+  for (int xi = 0; xi < nxst; ++xi) {
+    if (!failed && !mbar_wait(bar_x0 + (xi & 1) * 8, (xi >> 1) & 1)) {
+      failed = true;
+      report_status(kStatusActivationCopyTimeout);
     }
-    __syncthreads();
-    if (!active) continue;
-
-    for (int i0 = st; i0 < st + st_blocks; i0 += D) {
+    const uint16_t *xbuf = xs + (xi & 1) * plan.xrows * xstride;
+    const int c_lo = xi * (kXBlocks / CB);
+    const int c_hi = min(nchunks, c_lo + kXBlocks / CB);
+    if (active && !failed) {
+      for (int c = c_lo; c < c_hi; ++c) {
+        const int st = c % kStages;
+        if (!mbar_wait(bar_full0 + st * 8, (c / kStages) & 1)) {
+          failed = true;
+          report_status(kStatusWeightCopyTimeout);
+          break;
+        }
+        const unsigned char *stage = ring + st * plan.stage_bytes;
+        const int nb = min(CB, nblk - c * CB);
 #pragma unroll
-      for (int d = 0; d < D; ++d) {
-        const int i = i0 + d;
-        if (i < nblk) {
-          float acc[NT][4];
+        for (int cb = 0; cb < CB; ++cb) {
+          if (cb < nb) {
+            const int bi = c * CB + cb - xi * kXBlocks;  // block inside the x stage
+            uint32_t w[2 * B];
+            {
+              const uint32_t *blk = reinterpret_cast<const uint32_t *>(stage + cb * WBYTES);
 #pragma unroll
-          for (int nt = 0; nt < NT; ++nt)
-#pragma unroll
-            for (int e = 0; e < 4; ++e) acc[nt][e] = 0.f;
-
-#pragma unroll
-          for (int jj = 0; jj < 4; ++jj) {
-            uint32_t a_lo[4], a_hi[4];
-#pragma unroll
-            for (int q = 0; q < 4; ++q) {
-              a_lo[q] = decode_pair<B>(wbuf[d], 8 * jj + q);
-              a_hi[q] = decode_pair<B>(wbuf[d], 8 * jj + 4 + q);
-              if constexpr (BF16) {
-                a_lo[q] = h2_to_bf2(a_lo[q]);
-                a_hi[q] = h2_to_bf2(a_hi[q]);
+              for (int v = 0; v < BlockTraits<B>::NV; ++v) {
+                const uint4 q = *reinterpret_cast<const uint4 *>(blk + v * 128 + lane * 4);
+                w[4 * v + 0] = q.x;
+                w[4 * v + 1] = q.y;
+                w[4 * v + 2] = q.z;
+                w[4 * v + 3] = q.w;
+              }
+              if constexpr (BlockTraits<B>::TAIL == 2) {
+                const uint2 q = *reinterpret_cast<const uint2 *>(blk + BlockTraits<B>::NV * 128 + lane * 2);
+                w[4 * BlockTraits<B>::NV + 0] = q.x;
+                w[4 * BlockTraits<B>::NV + 1] = q.y;
               }
             }
+            const uint16_t *sblk = reinterpret_cast<const uint16_t *>(stage + CB * WBYTES + cb * SCB);
+
+            // lanes whose batch column does not exist read the last valid row: their
+            // accumulator columns are never written out
+            uint4 xb[4][NT];
 #pragma unroll
             for (int nt = 0; nt < NT; ++nt) {
-              uint4 xb = make_uint4(0u, 0u, 0u, 0u);
-              if (nt * 8 + g < mvalid)
-                xb = *reinterpret_cast<const uint4 *>(xs + (nt * 8 + g) * xstride + (i - st) * 128 + 32 * jj + 8 * t);
-              if constexpr (GS == -1) {
-                mma16816<BF16>(yacc[nt], a_lo, xb.x, xb.y);
-                mma16816<BF16>(yacc[nt], a_hi, xb.z, xb.w);
-              } else {
-                mma16816<BF16>(acc[nt], a_lo, xb.x, xb.y);
-                mma16816<BF16>(acc[nt], a_hi, xb.z, xb.w);
-              }
+              const int xrow = min(nt * 8 + g, mvalid - 1);
+#pragma unroll
+              for (int jj = 0; jj < 4; ++jj)
+                xb[jj][nt] = *reinterpret_cast<const uint4 *>(xbuf + xrow * xstride + bi * 128 + 32 * jj + 8 * t);
             }
-            if constexpr (GS == 32) {
-              const float slo = scale_to_float<BF16>(sbuf[d].lo[jj]);
-              const float shi = scale_to_float<BF16>(sbuf[d].hi[jj]);
+
+            // two accumulator sets so that consecutive mma do not wait on each other
+            float acc[2][NT][4];
+#pragma unroll
+            for (int h = 0; h < 2; ++h)
+#pragma unroll
+              for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) acc[h][nt][e] = 0.f;
+
+#pragma unroll
+            for (int jj = 0; jj < 4; ++jj) {
+              uint32_t a_lo[4], a_hi[4];
+#pragma unroll
+              for (int q = 0; q < 4; ++q) {
+                a_lo[q] = decode_pair<B>(w, 8 * jj + q);
+                a_hi[q] = decode_pair<B>(w, 8 * jj + 4 + q);
+                if constexpr (BF16) {
+                  a_lo[q] = h2_to_bf2(a_lo[q]);
+                  a_hi[q] = h2_to_bf2(a_hi[q]);
+                }
+              }
 #pragma unroll
               for (int nt = 0; nt < NT; ++nt) {
-                yacc[nt][0] = fmaf(slo, acc[nt][0], yacc[nt][0]);
-                yacc[nt][1] = fmaf(slo, acc[nt][1], yacc[nt][1]);
-                yacc[nt][2] = fmaf(shi, acc[nt][2], yacc[nt][2]);
-                yacc[nt][3] = fmaf(shi, acc[nt][3], yacc[nt][3]);
-                acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.f;
+                mma16816<BF16>(acc[0][nt], a_lo, xb[jj][nt].x, xb[jj][nt].y);
+                mma16816<BF16>(acc[1][nt], a_hi, xb[jj][nt].z, xb[jj][nt].w);
+              }
+              if constexpr (GS == 32) {
+                const float slo = scale_to_float<BF16>(sblk[jj * 16 + g]);
+                const float shi = scale_to_float<BF16>(sblk[jj * 16 + g + 8]);
+#pragma unroll
+                for (int nt = 0; nt < NT; ++nt) {
+                  yacc[nt][0] = fmaf(slo, acc[0][nt][0] + acc[1][nt][0], yacc[nt][0]);
+                  yacc[nt][1] = fmaf(slo, acc[0][nt][1] + acc[1][nt][1], yacc[nt][1]);
+                  yacc[nt][2] = fmaf(shi, acc[0][nt][2] + acc[1][nt][2], yacc[nt][2]);
+                  yacc[nt][3] = fmaf(shi, acc[0][nt][3] + acc[1][nt][3], yacc[nt][3]);
+#pragma unroll
+                  for (int e = 0; e < 4; ++e) acc[0][nt][e] = acc[1][nt][e] = 0.f;
+                }
               }
             }
-          }
-          if constexpr (GS == 128) {
-            const float slo = scale_to_float<BF16>(sbuf[d].lo[0]);
-            const float shi = scale_to_float<BF16>(sbuf[d].hi[0]);
+            if constexpr (GS == 128) {
+              const float slo = scale_to_float<BF16>(sblk[g]);
+              const float shi = scale_to_float<BF16>(sblk[g + 8]);
 #pragma unroll
-            for (int nt = 0; nt < NT; ++nt) {
-              yacc[nt][0] = fmaf(slo, acc[nt][0], yacc[nt][0]);
-              yacc[nt][1] = fmaf(slo, acc[nt][1], yacc[nt][1]);
-              yacc[nt][2] = fmaf(shi, acc[nt][2], yacc[nt][2]);
-              yacc[nt][3] = fmaf(shi, acc[nt][3], yacc[nt][3]);
+              for (int nt = 0; nt < NT; ++nt) {
+                yacc[nt][0] = fmaf(slo, acc[0][nt][0] + acc[1][nt][0], yacc[nt][0]);
+                yacc[nt][1] = fmaf(slo, acc[0][nt][1] + acc[1][nt][1], yacc[nt][1]);
+                yacc[nt][2] = fmaf(shi, acc[0][nt][2] + acc[1][nt][2], yacc[nt][2]);
+                yacc[nt][3] = fmaf(shi, acc[0][nt][3] + acc[1][nt][3], yacc[nt][3]);
+              }
+            }
+            if constexpr (GS == -1) {
+#pragma unroll
+              for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) yacc[nt][e] += acc[0][nt][e] + acc[1][nt][e];
             }
           }
-          if (i + D < nblk) {
-            load_block<B>(wbase + static_cast<size_t>(i + D) * BW, lane, wbuf[d]);
-            load_scales<GS>(p.s, tile, kb_lo + i + D, groups, lane, sbuf[d]);
-          }
         }
+        // the stage has been read into registers by every lane: refill it
+        __syncwarp();
+        if (lane == 0 && c + kStages < nchunks) issue_chunk(c + kStages);
       }
+    }
+    if (xi + 2 < nxst) {
+      __syncthreads();  // every warp is done with this activation buffer
+      if (threadIdx.x == 0) issue_x(xi + 2);
     }
   }
 
@@ -291,29 +385,23 @@ __global__ void __launch_bounds__(256) gemv_kernel(const GemvParams p) {
 // ----------------------------------------------------------------------------
 // host side
 // ----------------------------------------------------------------------------
-template <int B> struct Depth {
-  static constexpr int value = (B == 2) ? 8 : (B == 3) ? 5 : (B == 4) ? 4 : (B == 6) ? 3 : 2;
-};
-
 static int g_sm_count = 0;
 
 template <int B, int GS, bool BF16, int NT>
 static int launch_gemv(const GemvParams &p, int R, cudaStream_t stream, bool pdl) {
-  constexpr int D = Depth<B>::value;
-  auto kernel = gemv_kernel<B, GS, BF16, NT, D>;
+  auto kernel = gemv_kernel<B, GS, BF16, NT>;
   const int S = p.split;
   const int max_nblk = (p.kblocks + S - 1) / S;
-  constexpr int XB = D * ((16 + D - 1) / D);
-  const int stage_blocks = max_nblk < XB ? max_nblk : XB;
-  const size_t smem = static_cast<size_t>(NT * 8) * (stage_blocks * 128 + 32) * 2 + static_cast<size_t>(NT * 8) * (R * 16 + 4) * 4;
+  const SmemPlan plan = make_plan<B, GS, NT>(R, p.M, max_nblk);
+  const size_t smem = static_cast<size_t>(plan.total);
   if (smem > 48 * 1024) {
-    // at most NT*8 = 16 rows x (20 blocks x 256 B + 64 B) + partial sums < 96 KiB: opt in once per device
+    // worst case: 2 x 16 rows x 2112 B of activations + 8 warps x 4 stages x 2.5 KB < 160 KiB: opt in once per device
     static bool opted_in[64] = {};
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess) return MG_ERR_CUDA;
     if (dev < 0 || dev >= 64) return MG_ERR_BAD_ARG;
     if (!opted_in[dev]) {
-      cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
+      cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
       if (e != cudaSuccess) return MG_ERR_CUDA;
       opted_in[dev] = true;
     }
@@ -367,32 +455,19 @@ static int launch_gemv_group(const GemvParams &p, int R, int group_size, bool bf
   }
 }
 
-// Pick warps per CTA (R) and CTAs per cluster along K (S): enough CTAs to cover
-// every SM a few times over, a K slice of at least two blocks per warp where the
-// shape allows, and R as large as that permits so that the staged activations
-// are reused by many row tiles.
+// Pick warps per CTA (R) and CTAs per cluster along K (S).  Measured on B200: the
+// kernel wants about 12-14 warps per SM in total (tiles * S close to 2048), S no
+// larger than that needs (every extra CTA pays barrier set-up, an activation copy and
+// the cluster reduction), and R as large as still leaves one CTA per SM, so that the
+// staged activations are shared by many row tiles.
 void gemv_pick_config(int tiles, int kblocks, int sm_count, int *R_out, int *S_out) {
-  const int want = 2 * sm_count;
-  int bestR = 8, bestS = 1;
-  long long best_score = -1;
-  for (int R = 8; R >= 2; R >>= 1) {
-    for (int S = 1; S <= 8; S <<= 1) {
-      if (S > kblocks) break;
-      const int per_warp = kblocks / S;
-      if (S > 1 && per_warp < 2) break;
-      const long long ctas = static_cast<long long>((tiles + R - 1) / R) * S;
-      const long long filled = ctas >= want ? want : ctas;
-      // prefer filling the machine, then larger R, then smaller S
-      const long long score = filled * 1000 + R * 10 - S;
-      if (score > best_score) {
-        best_score = score;
-        bestR = R;
-        bestS = S;
-      }
-    }
-  }
-  *R_out = bestR;
-  *S_out = bestS;
+  const int want_warps = 14 * sm_count;
+  int S = 1;
+  while (S < 8 && tiles * S * 2 <= want_warps && S * 2 <= kblocks) S <<= 1;
+  int R = 8;
+  while (R > 1 && static_cast<long long>((tiles + R - 1) / R) * S < sm_count) R >>= 1;
+  *R_out = R;
+  *S_out = S;
 }
 
 int gemv_launch(int bitwidth, int group_size, int N, int K, int M, const void *w, const void *s, const void *x,
@@ -427,5 +502,7 @@ int gemv_launch(int bitwidth, int group_size, int N, int K, int M, const void *w
     default: return MG_ERR_BAD_ARG;
   }
 }
+
+MG_DEFINE_STATUS_ACCESSOR(gemv_device_status)
 
 }  // namespace mg

@@ -18,6 +18,8 @@ void gemv_pick_config(int tiles, int kblocks, int sm_count, int *R_out, int *S_o
 int gemv_launch(int bitwidth, int group_size, int N, int K, int M, const void *w, const void *s, const void *x,
                 void *y, bool bf16, bool pdl, int R_override, int S_override, cudaStream_t stream);
 
+int gemv_device_status(int *status_out, int reset);
+
 // pack.cu
 int slice_launch(const uint8_t *in, uint8_t *out, long long numel, int master_bitwidth, int bitwidth,
                  cudaStream_t stream);

@@ -77,8 +77,8 @@ def test_dequant_fake_linear_golden(lib, cuda, golden, b):
     zp = torch.from_numpy(golden["fl_zero"])
     packed = torch.ops.matgptq_cuda.slice_pack_matgptq_qweights(q, n, k, 8, b, 128, 1)
     out = torch.empty(n, k, dtype=torch.float16, device=cuda)
-    st = lib.matgptq_b200_dequantize(packed.data_ptr(), _reorder(sc, n, k, 128).data_ptr(),
-                                     _reorder(zp, n, k, 128).data_ptr(), out.data_ptr(), n, k, b, 128, 1,
+    s_r, z_r = _reorder(sc, n, k, 128), _reorder(zp, n, k, 128)  # keep alive across the raw-pointer call
+    st = lib.matgptq_b200_dequantize(packed.data_ptr(), s_r.data_ptr(), z_r.data_ptr(), out.data_ptr(), n, k, b, 128, 1,
                                      torch.cuda.current_stream().cuda_stream)
     assert st == 0
     torch.cuda.synchronize()

@@ -137,7 +137,8 @@ def test_input_views_and_errors(cuda):
     with pytest.raises(RuntimeError, match="wrong size"):
         torch.ops.matgptq_cuda.matmul_matgptq(x, packed[:-1], scales_r, n_out, n_in, b, 128, flag)
     with pytest.raises(RuntimeError, match="bitwidth"):
-        torch.ops.matgptq_cuda.matmul_matgptq(x, packed, scales_r, n_out, n_in, 5, 128, flag)
+        wrong = torch.zeros(5 * n_out * n_in // 32, dtype=torch.uint32, device=cuda)
+        torch.ops.matgptq_cuda.matmul_matgptq(x, wrong, scales_r, n_out, n_in, 5, 128, flag)
     with pytest.raises(RuntimeError, match="CUDA"):
         torch.ops.matgptq_cuda.matmul_matgptq(x.cpu(), packed, scales_r, n_out, n_in, b, 128, flag)
     empty = torch.ops.matgptq_cuda.matmul_matgptq(x[:0], packed, scales_r, n_out, n_in, b, 128, flag)
