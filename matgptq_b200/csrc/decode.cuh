@@ -2,11 +2,16 @@
 //
 // Replaces the reference's plane merge + magic-number converters
 // (csrc/matgptq_gemm.cu:90-295).  A pair of b-bit codes stored at bit offset p
-// of both halves of a word becomes, with ONE LOP3, the half2
-// (1024 + c_lo*2^p, 1024 + c_hi*2^p); one HFMA2 with constants (2^-p,
-// -(1024*2^-p + Z)) turns it into the exact integers (c - Z), Z = 2^(b-1).
-// Fields whose top bit would leave the 10-bit fp16 mantissa are reached through
-// one shared right shift of the word.
+// of both halves of a word is isolated by ONE LOP3 (field_pair).  Left as it is,
+// the result is the half2 of fp16 subnormals (c_lo, c_hi) * 2^(p-24), which the
+// tensor core multiplies exactly: the GEMV feeds these straight into mma and
+// settles the factor 2^(24-p) and the zero point once per group in fp32.  With
+// 0x6400 OR-ed in by the same LOP3 it is (1024 + c*2^p), and one HFMA2 with
+// constants (2^-p, -(1024*2^-p + Z)) gives the exact integers (c - Z), Z = 2^(b-1)
+// (decode_pair), for the paths that need dense weights.  Fields whose top bit
+// would leave the 10-bit fp16 mantissa are reached through one shared right shift
+// of the word.  On B200 LOP3, SHF, PRMT and HFMA2 all issue at half rate
+// (16 lanes per clock and scheduler), which is why the GEMV avoids the HFMA2.
 #pragma once
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
@@ -67,59 +72,60 @@ template <int Z> __device__ __forceinline__ uint32_t normalize(uint32_t x, int p
   }
 }
 
+// Raw field pair P of a lane: both codes isolated at bit offset kstep_offset<B>(P >> 2)
+// of their 16-bit halves, every other bit zero.  Read as half2 these are the subnormals
+// code * 2^(offset - 24).  `orv` is OR-ed in by the same instruction (0, or the magic 0x64006400).
+template <int B> __device__ __forceinline__ uint32_t field_pair(const uint32_t (&w)[2 * B], int P, uint32_t orv) {
+  const int i = P >> 2, r = P & 3;
+  if constexpr (B == 2) {
+    const uint32_t W = w[r] >> (6 * (i / 3));
+    return lop3_and_or(W, 0x00030003u << (2 * (i % 3)), orv);
+  } else if constexpr (B == 4) {
+    const int q = i & 3;
+    const uint32_t W = w[4 * (i >> 2) + r] >> (8 * (q >> 1));
+    return lop3_and_or(W, 0x000F000Fu << (4 * (q & 1)), orv);
+  } else if constexpr (B == 8) {
+    const uint32_t W = w[4 * (i >> 1) + r];
+    if ((i & 1) == 0) return lop3_and_or(W, 0x00FF00FFu, orv);
+    uint32_t x;
+    asm("prmt.b32 %0, %1, %2, 0x7351;" : "=r"(x) : "r"(W), "r"(orv));  // bytes (W.b1, orv.b1, W.b3, orv.b3)
+    return x;
+  } else if constexpr (B == 3) {
+    if (i < 6) {
+      const int e = 4 * (i % 3) + r;
+      const int u = e / 6, f = e % 6;
+      const uint32_t W = w[3 * u + (f >> 1)] >> ((f & 1) ? 9 : 0);
+      return lop3_and_or(W, 0x00070007u << (i < 3 ? 0 : 3), orv);
+    }
+    const int u = i - 6;
+    if (r < 3) return lop3_and_or(w[3 * u + r], 0x01C001C0u, orv);
+    uint32_t x = lop3_and_or(w[3 * u] >> 9, 0x00400040u, orv);
+    x = lop3_and_or(w[3 * u + 1] >> 8, 0x00800080u, x);
+    x = lop3_and_or(w[3 * u + 2] >> 7, 0x01000100u, x);
+    return x;
+  } else {
+    static_assert(B == 6, "bitwidth must be one of 2, 3, 4, 6, 8");
+    const int u = i >> 1, e = 4 * (i & 1) + r;
+    if (e < 6) {
+      const uint32_t W = w[3 * u + (e >> 1)] >> (6 * (e & 1));
+      return lop3_and_or(W, 0x003F003Fu, orv);
+    }
+    uint32_t x;
+    if (e == 6) {
+      x = lop3_and_or(w[3 * u] >> 12, 0x000F000Fu, orv);
+      x = lop3_and_or(w[3 * u + 1] >> 8, 0x00300030u, x);
+    } else {
+      x = lop3_and_or(w[3 * u + 1] >> 14, 0x00030003u, orv);
+      x = lop3_and_or(w[3 * u + 2] >> 10, 0x003C003Cu, x);
+    }
+    return x;
+  }
+}
+
 // Decoded pair P of a lane as half2 of exact integers (code - Z).
 template <int B> __device__ __forceinline__ uint32_t decode_pair(const uint32_t (&w)[2 * B], int P) {
   constexpr int Z = BlockTraits<B>::ZERO;
-  if constexpr (B == 2) {
-    const int q = P & 7;
-    const uint32_t W = w[P >> 3];
-    if (q < 5) return normalize<Z>(lop3_and_or(W, 0x00030003u << (2 * q), kMagic), 2 * q);
-    return normalize<Z>(lop3_and_or(W >> 10, 0x00030003u << (2 * (q - 5)), kMagic), 2 * (q - 5));
-  } else if constexpr (B == 4) {
-    const int q = P & 3;
-    const uint32_t W = w[P >> 2];
-    if (q < 2) return normalize<Z>(lop3_and_or(W, 0x000F000Fu << (4 * q), kMagic), 4 * q);
-    return normalize<Z>(lop3_and_or(W >> 8, 0x000F000Fu << (4 * (q - 2)), kMagic), 4 * (q - 2));
-  } else if constexpr (B == 8) {
-    const uint32_t W = w[P >> 1];
-    uint32_t x;
-    if ((P & 1) == 0) {
-      x = lop3_and_or(W, 0x00FF00FFu, kMagic);
-    } else {
-      // bytes (W.b1, 0x64, W.b3, 0x64)
-      asm("prmt.b32 %0, %1, %2, 0x7351;" : "=r"(x) : "r"(W), "r"(kMagic));
-    }
-    return normalize<Z>(x, 0);
-  } else if constexpr (B == 3) {
-    const int u = P >> 4, p = P & 15;
-    if (p < 15) {
-      const int q = p % 5;
-      const uint32_t W = w[3 * u + p / 5];
-      if (q < 3) return normalize<Z>(lop3_and_or(W, 0x00070007u << (3 * q), kMagic), 3 * q);
-      return normalize<Z>(lop3_and_or(W >> 9, 0x00070007u << (3 * (q - 3)), kMagic), 3 * (q - 3));
-    }
-    uint32_t x = lop3_and_or(w[3 * u] >> 15, 0x00010001u, kMagic);
-    x = lop3_and_or(w[3 * u + 1] >> 14, 0x00020002u, x);
-    x = lop3_and_or(w[3 * u + 2] >> 13, 0x00040004u, x);
-    return normalize<Z>(x, 0);
-  } else {
-    static_assert(B == 6, "bitwidth must be one of 2, 3, 4, 6, 8");
-    const int u = P >> 3, p = P & 7;
-    if (p < 6) {
-      const uint32_t W = w[3 * u + (p >> 1)];
-      if ((p & 1) == 0) return normalize<Z>(lop3_and_or(W, 0x003F003Fu, kMagic), 0);
-      return normalize<Z>(lop3_and_or(W >> 6, 0x003F003Fu, kMagic), 0);
-    }
-    uint32_t x;
-    if (p == 6) {
-      x = lop3_and_or(w[3 * u] >> 12, 0x000F000Fu, kMagic);
-      x = lop3_and_or(w[3 * u + 1] >> 8, 0x00300030u, x);
-    } else {
-      x = lop3_and_or(w[3 * u + 1] >> 14, 0x00030003u, kMagic);
-      x = lop3_and_or(w[3 * u + 2] >> 10, 0x003C003Cu, x);
-    }
-    return normalize<Z>(x, 0);
-  }
+  return normalize<Z>(field_pair<B>(w, P, kMagic), kstep_offset<B>(P >> 2));
 }
 
 // half2 of small exact integers -> bfloat162 of the same integers.

@@ -48,20 +48,34 @@ struct GemvParams {
   int split;    // CTAs per cluster along K
 };
 
-template <bool BF16>
+// D = A*B + C on the tensor pipe, fp16 operands, fp32 accumulate.  ZERO_C starts a new
+// accumulation without first clearing registers.
+template <bool ZERO_C>
 __device__ __forceinline__ void mma16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
-  if constexpr (BF16) {
-    asm(
-        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+  if constexpr (ZERO_C) {
+    asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+        : "=f"(c[0]), "=f"(c[1]), "=f"(c[2]), "=f"(c[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "f"(0.f));
   } else {
-    asm(
-        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+    asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
         : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
         : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
   }
 }
+
+// Accumulator chains of a block.  A k-step whose fields decode at bit offset p carries
+// the factor 2^p, so k-steps are spread over chains by offset; bitwidths with a single
+// offset still use two chains so that consecutive mma do not depend on each other.
+template <int B> struct Chains {
+  static constexpr int N = (B == 2 || B == 3) ? 3 : 2;
+  __host__ __device__ static constexpr int of(int i) { return (B == 2) ? i % 3 : (B == 3) ? (i < 3 ? 0 : (i < 6 ? 1 : 2)) : (i & 1); }
+  __host__ __device__ static constexpr bool first(int i) { return (B == 3) ? (i == 0 || i == 3 || i == 6) : (i < N); }
+  // 2^-offset of chain c
+  __host__ __device__ static constexpr float inv_factor(int c) {
+    return (B == 2) ? (c == 0 ? 1.f : (c == 1 ? 0.25f : 0.0625f))
+                    : (B == 3) ? (c == 0 ? 1.f : (c == 1 ? 0.125f : 0.015625f)) : (B == 4) ? (c == 0 ? 1.f : 0.0625f) : 1.f;
+  }
+};
 
 template <bool BF16> __device__ __forceinline__ float scale_to_float(uint16_t v) {
   if constexpr (BF16) {
@@ -97,8 +111,8 @@ template <int NT> struct XBlocks {
 
 // Shared-memory plan of one CTA, computed identically on host and device.
 struct SmemPlan {
-  int xrows, xstride_h, rstride, stage_bytes, scale_bytes_per_block;
-  int off_bars, off_x, off_red, off_ring, total;
+  int xrows, xstride_h, rstride, stage_bytes, scale_bytes_per_block, sums_per_block;
+  int off_bars, off_x, off_sums, off_red, off_ring, total;
 };
 
 template <int B, int GS, int NT>
@@ -112,7 +126,10 @@ __host__ __device__ inline SmemPlan make_plan(int R, int M, int max_nblk) {
   p.stage_bytes = ChunkBlocks<B>::value * (BlockTraits<B>::WORDS * 4 + p.scale_bytes_per_block);
   p.off_bars = 0;
   p.off_x = 128 * ((8 * (R * kStages + 2) + 127) / 128);
-  p.off_red = p.off_x + 2 * p.xrows * p.xstride_h * 2;
+  // per activation stage: for every block and group the sum of each activation row (fp32)
+  p.sums_per_block = ((GS == 32) ? 4 : 1) * NT * 8;
+  p.off_sums = p.off_x + 2 * p.xrows * p.xstride_h * 2;
+  p.off_red = p.off_sums + 2 * XBlocks<NT>::value * p.sums_per_block * 4;
   p.off_ring = 128 * ((p.off_red + NT * 8 * p.rstride * 4 + 127) / 128);
   p.total = p.off_ring + R * kStages * p.stage_bytes;
   return p;
@@ -121,7 +138,7 @@ __host__ __device__ inline SmemPlan make_plan(int R, int M, int max_nblk) {
 // B: bitwidth, GS: group size (-1, 32, 128), BF16: activation/scale/output type,
 // NT: batch tiles of 8 rows handled per pass.
 template <int B, int GS, bool BF16, int NT>
-__global__ void __launch_bounds__(256) gemv_kernel(const GemvParams p) {
+__global__ void __launch_bounds__(256, 2) gemv_kernel(const GemvParams p) {
   extern __shared__ __align__(128) unsigned char smem_raw[];
 
   const int lane = threadIdx.x & 31;
@@ -149,7 +166,6 @@ __global__ void __launch_bounds__(256) gemv_kernel(const GemvParams p) {
   const uint32_t smem_base = smem_u32(smem_raw);
   const uint32_t bar_full0 = smem_base + plan.off_bars + warp * kStages * 8;  // this warp's ring barriers
   const uint32_t bar_x0 = smem_base + plan.off_bars + R * kStages * 8;        // two activation barriers
-  const uint16_t *xs = reinterpret_cast<const uint16_t *>(smem_raw + plan.off_x);
   float *red = reinterpret_cast<float *>(smem_raw + plan.off_red);
   const unsigned char *ring = smem_raw + plan.off_ring + warp * kStages * plan.stage_bytes;
   const uint32_t ring_u32 = smem_base + plan.off_ring + warp * kStages * plan.stage_bytes;
@@ -204,11 +220,16 @@ __global__ void __launch_bounds__(256) gemv_kernel(const GemvParams p) {
     if (nxst > 1) issue_x(1);
   }
 
+  // y accumulates sum_g s_g * (sum_k code*x - Z*sum_k x) in units of 2^-24 (the subnormal scale)
   float yacc[NT][4];
 #pragma unroll
   for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
     for (int e = 0; e < 4; ++e) yacc[nt][e] = 0.f;
+
+  constexpr int NCH = Chains<B>::N;
+  constexpr float kNegZero = -static_cast<float>(BlockTraits<B>::ZERO) * 5.9604644775390625e-08f;  // -Z * 2^-24
+  float *sums = reinterpret_cast<float *>(smem_raw + plan.off_sums);
 
   bool failed = false;
   for (int xi = 0; xi < nxst; ++xi) {
@@ -216,7 +237,60 @@ __global__ void __launch_bounds__(256) gemv_kernel(const GemvParams p) {
       failed = true;
       report_status(kStatusActivationCopyTimeout);
     }
-    const uint16_t *xbuf = xs + (xi & 1) * plan.xrows * xstride;
+    uint16_t *xbuf = reinterpret_cast<uint16_t *>(smem_raw + plan.off_x) + (xi & 1) * plan.xrows * xstride;
+    float *xsum = sums + (xi & 1) * kXBlocks * plan.sums_per_block;
+    const int st_blocks = min(kXBlocks, nblk - xi * kXBlocks);
+
+    // bf16 activations become fp16 in place (saturating at +-65504): the type the tensor
+    // pipe multiplies with the fp16 codes.
+    if constexpr (BF16) {
+      const int chunks_per_row = st_blocks * 16;  // 16-byte chunks
+      for (int ci = threadIdx.x; ci < mvalid * chunks_per_row; ci += blockDim.x) {
+        const int m = ci / chunks_per_row, cc = ci - m * chunks_per_row;
+        uint4 *ptr = reinterpret_cast<uint4 *>(xbuf + m * xstride + cc * 8);
+        uint4 v = *ptr;
+        uint32_t *vw = reinterpret_cast<uint32_t *>(&v);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          float lo = __uint_as_float(vw[e] << 16), hi = __uint_as_float(vw[e] & 0xFFFF0000u);
+          lo = fminf(fmaxf(lo, -65504.f), 65504.f);
+          hi = fminf(fmaxf(hi, -65504.f), 65504.f);
+          vw[e] = h2_bits(__floats2half2_rn(lo, hi));
+        }
+        *ptr = v;
+      }
+      __syncthreads();
+    }
+
+    // Row sums of the activations per group, times -Z*2^-24: the zero-point term of every
+    // output this CTA produces from this stage.  One warp per block multiplies the same B
+    // fragments the main loop uses with an A fragment of ones, so the sums come out in the
+    // accumulator layout (batch columns 2t, 2t+1) and need no shuffles.
+    for (int blk = warp; blk < st_blocks; blk += R) {
+      const uint32_t ones[4] = {0x3C003C00u, 0x3C003C00u, 0x3C003C00u, 0x3C003C00u};
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt) {
+        const int xrow = min(nt * 8 + g, mvalid - 1);
+        float sacc[4];
+#pragma unroll
+        for (int jj = 0; jj < 4; ++jj) {
+          const uint4 xv = *reinterpret_cast<const uint4 *>(xbuf + xrow * xstride + blk * 128 + 32 * jj + 8 * t);
+          if (GS == 32 || jj == 0)
+            mma16816<true>(sacc, ones, xv.x, xv.y);
+          else
+            mma16816<false>(sacc, ones, xv.x, xv.y);
+          mma16816<false>(sacc, ones, xv.z, xv.w);
+          if (GS == 32 && g == 0)
+            *reinterpret_cast<float2 *>(xsum + blk * plan.sums_per_block + jj * (NT * 8) + nt * 8 + 2 * t) =
+                make_float2(kNegZero * sacc[0], kNegZero * sacc[1]);
+        }
+        if (GS != 32 && g == 0)
+          *reinterpret_cast<float2 *>(xsum + blk * plan.sums_per_block + nt * 8 + 2 * t) =
+              make_float2(kNegZero * sacc[0], kNegZero * sacc[1]);
+      }
+    }
+    __syncthreads();
+
     const int c_lo = xi * (kXBlocks / CB);
     const int c_hi = min(nchunks, c_lo + kXBlocks / CB);
     if (active && !failed) {
@@ -251,6 +325,7 @@ __global__ void __launch_bounds__(256) gemv_kernel(const GemvParams p) {
               }
             }
             const uint16_t *sblk = reinterpret_cast<const uint16_t *>(stage + CB * WBYTES + cb * SCB);
+            const float *bsum = xsum + bi * plan.sums_per_block;
 
             // lanes whose batch column does not exist read the last valid row: their
             // accumulator columns are never written out
@@ -263,62 +338,67 @@ __global__ void __launch_bounds__(256) gemv_kernel(const GemvParams p) {
                 xb[jj][nt] = *reinterpret_cast<const uint4 *>(xbuf + xrow * xstride + bi * 128 + 32 * jj + 8 * t);
             }
 
-            // two accumulator sets so that consecutive mma do not wait on each other
-            float acc[2][NT][4];
+            if constexpr (GS == 32) {
+              // one group per pair of k-steps: each k-step gets its own accumulator
 #pragma unroll
-            for (int h = 0; h < 2; ++h)
+              for (int jj = 0; jj < 4; ++jj) {
+                float d0[NT][4], d1[NT][4];
+                uint32_t a0[4], a1[4];
 #pragma unroll
-              for (int nt = 0; nt < NT; ++nt)
-#pragma unroll
-                for (int e = 0; e < 4; ++e) acc[h][nt][e] = 0.f;
-
-#pragma unroll
-            for (int jj = 0; jj < 4; ++jj) {
-              uint32_t a_lo[4], a_hi[4];
-#pragma unroll
-              for (int q = 0; q < 4; ++q) {
-                a_lo[q] = decode_pair<B>(w, 8 * jj + q);
-                a_hi[q] = decode_pair<B>(w, 8 * jj + 4 + q);
-                if constexpr (BF16) {
-                  a_lo[q] = h2_to_bf2(a_lo[q]);
-                  a_hi[q] = h2_to_bf2(a_hi[q]);
+                for (int q = 0; q < 4; ++q) {
+                  a0[q] = field_pair<B>(w, 8 * jj + q, 0u);
+                  a1[q] = field_pair<B>(w, 8 * jj + 4 + q, 0u);
                 }
-              }
-#pragma unroll
-              for (int nt = 0; nt < NT; ++nt) {
-                mma16816<BF16>(acc[0][nt], a_lo, xb[jj][nt].x, xb[jj][nt].y);
-                mma16816<BF16>(acc[1][nt], a_hi, xb[jj][nt].z, xb[jj][nt].w);
-              }
-              if constexpr (GS == 32) {
+                const float f0 = 1.f / static_cast<float>(1 << kstep_offset<B>(2 * jj));
+                const float f1 = 1.f / static_cast<float>(1 << kstep_offset<B>(2 * jj + 1));
                 const float slo = scale_to_float<BF16>(sblk[jj * 16 + g]);
                 const float shi = scale_to_float<BF16>(sblk[jj * 16 + g + 8]);
 #pragma unroll
                 for (int nt = 0; nt < NT; ++nt) {
-                  yacc[nt][0] = fmaf(slo, acc[0][nt][0] + acc[1][nt][0], yacc[nt][0]);
-                  yacc[nt][1] = fmaf(slo, acc[0][nt][1] + acc[1][nt][1], yacc[nt][1]);
-                  yacc[nt][2] = fmaf(shi, acc[0][nt][2] + acc[1][nt][2], yacc[nt][2]);
-                  yacc[nt][3] = fmaf(shi, acc[0][nt][3] + acc[1][nt][3], yacc[nt][3]);
-#pragma unroll
-                  for (int e = 0; e < 4; ++e) acc[0][nt][e] = acc[1][nt][e] = 0.f;
+                  mma16816<true>(d0[nt], a0, xb[jj][nt].x, xb[jj][nt].y);
+                  mma16816<true>(d1[nt], a1, xb[jj][nt].z, xb[jj][nt].w);
+                  const float2 zs = *reinterpret_cast<const float2 *>(bsum + jj * (NT * 8) + nt * 8 + 2 * t);
+                  yacc[nt][0] = fmaf(slo, fmaf(d1[nt][0], f1, fmaf(d0[nt][0], f0, zs.x)), yacc[nt][0]);
+                  yacc[nt][1] = fmaf(slo, fmaf(d1[nt][1], f1, fmaf(d0[nt][1], f0, zs.y)), yacc[nt][1]);
+                  yacc[nt][2] = fmaf(shi, fmaf(d1[nt][2], f1, fmaf(d0[nt][2], f0, zs.x)), yacc[nt][2]);
+                  yacc[nt][3] = fmaf(shi, fmaf(d1[nt][3], f1, fmaf(d0[nt][3], f0, zs.y)), yacc[nt][3]);
                 }
               }
-            }
-            if constexpr (GS == 128) {
-              const float slo = scale_to_float<BF16>(sblk[g]);
-              const float shi = scale_to_float<BF16>(sblk[g + 8]);
+            } else {
+              float acc[NCH][NT][4];
+#pragma unroll
+              for (int i = 0; i < 8; ++i) {
+                uint32_t a[4];
+#pragma unroll
+                for (int q = 0; q < 4; ++q) a[q] = field_pair<B>(w, 4 * i + q, 0u);
+                #pragma unroll
+                for (int nt = 0; nt < NT; ++nt) {
+                  const uint32_t b0 = (i & 1) ? xb[i >> 1][nt].z : xb[i >> 1][nt].x;
+                  const uint32_t b1 = (i & 1) ? xb[i >> 1][nt].w : xb[i >> 1][nt].y;
+                  if (Chains<B>::first(i))
+                    mma16816<true>(acc[Chains<B>::of(i)][nt], a, b0, b1);
+                  else
+                    mma16816<false>(acc[Chains<B>::of(i)][nt], a, b0, b1);
+                }
+              }
+              float slo = 1.f, shi = 1.f;
+              if constexpr (GS == 128) {
+                slo = scale_to_float<BF16>(sblk[g]);
+                shi = scale_to_float<BF16>(sblk[g + 8]);
+              }
 #pragma unroll
               for (int nt = 0; nt < NT; ++nt) {
-                yacc[nt][0] = fmaf(slo, acc[0][nt][0] + acc[1][nt][0], yacc[nt][0]);
-                yacc[nt][1] = fmaf(slo, acc[0][nt][1] + acc[1][nt][1], yacc[nt][1]);
-                yacc[nt][2] = fmaf(shi, acc[0][nt][2] + acc[1][nt][2], yacc[nt][2]);
-                yacc[nt][3] = fmaf(shi, acc[0][nt][3] + acc[1][nt][3], yacc[nt][3]);
+                const float2 zs = *reinterpret_cast<const float2 *>(bsum + nt * 8 + 2 * t);
+                float tsum[4] = {zs.x, zs.y, zs.x, zs.y};
+#pragma unroll
+                for (int ch = 0; ch < NCH; ++ch)
+#pragma unroll
+                  for (int e = 0; e < 4; ++e) tsum[e] = fmaf(acc[ch][nt][e], Chains<B>::inv_factor(ch), tsum[e]);
+                yacc[nt][0] = fmaf(slo, tsum[0], yacc[nt][0]);
+                yacc[nt][1] = fmaf(slo, tsum[1], yacc[nt][1]);
+                yacc[nt][2] = fmaf(shi, tsum[2], yacc[nt][2]);
+                yacc[nt][3] = fmaf(shi, tsum[3], yacc[nt][3]);
               }
-            }
-            if constexpr (GS == -1) {
-#pragma unroll
-              for (int nt = 0; nt < NT; ++nt)
-#pragma unroll
-                for (int e = 0; e < 4; ++e) yacc[nt][e] += acc[0][nt][e] + acc[1][nt][e];
             }
           }
         }
@@ -329,14 +409,19 @@ __global__ void __launch_bounds__(256) gemv_kernel(const GemvParams p) {
     }
     if (xi + 2 < nxst) {
       __syncthreads();  // every warp is done with this activation buffer
-      if (threadIdx.x == 0) issue_x(xi + 2);
+      if (threadIdx.x == 0) {
+        // the buffer was read (and, for bf16, rewritten) through the generic proxy
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        issue_x(xi + 2);
+      }
     }
   }
 
   if (active) {
     // 2^(8-b) (exact) and, for one scale per row, the row scale, both in fp32
-    // (csrc/matgptq_gemm.cu:615-633, 943-949).
-    float mlo = static_cast<float>(1 << (8 - B)), mhi = mlo;
+    // (csrc/matgptq_gemm.cu:615-633, 943-949), together with 2^24 that undoes the
+    // subnormal encoding of the codes.
+    float mlo = static_cast<float>(1 << (8 - B)) * 16777216.f, mhi = mlo;  // 2^(8-b) and the subnormal scale 2^24
     if constexpr (GS == -1) {
       mlo *= scale_to_float<BF16>(ldg_u16(p.s + static_cast<size_t>(tile) * 16 + g));
       mhi *= scale_to_float<BF16>(ldg_u16(p.s + static_cast<size_t>(tile) * 16 + g + 8));

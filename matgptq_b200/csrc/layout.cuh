@@ -16,8 +16,14 @@
 //     loads: word j of lane l sits at (j/4)*128 + l*4 + j%4; the two words of a
 //     3-bit block that do not fill a 16-byte vector follow as 8 bytes per lane.
 //   * In a word the two codes of a pair sit at the same bit offset of the low
-//     and the high 16-bit half, so that one LOP3 turns them into a half2 of
-//     (1024 + code * 2^offset) (the fp16 "magic number" conversion).
+//     and the high 16-bit half, so that ONE logic instruction (after at most one
+//     shared shift of the word) isolates them as a half2 whose halves are the fp16
+//     subnormals code * 2^(offset-24); the tensor core multiplies subnormals
+//     exactly.  OR-ing 0x6400 into the same bits gives (1024 + code * 2^offset),
+//     the classic magic-number form, where exact integers are wanted instead.
+//   * The four A registers of one mma k-step always come from fields at the same
+//     bit offset, so a whole k-step carries one power-of-two factor; k-steps with
+//     different factors accumulate into different accumulators.
 //   * 3-bit and 6-bit codes do not tile 16 bits: five (two) fields per half are
 //     stored directly and the spare bits of three consecutive words carry one
 //     (two) more pair(s).
@@ -74,19 +80,32 @@ struct Piece {
 
 template <int B> MG_HD int code_pieces(int P, int h, Piece (&out)[3]) {
   const int hb = 16 * h;
+  const int i = P >> 2, r = P & 3;  // mma k-step and A register
   if (B == 2) {
-    out[0] = {P >> 3, hb + 2 * (P & 7), 2, 0};
+    // one 16-byte vector per lane: register r of k-step i is field i of word r
+    out[0] = {r, hb + 2 * i, 2, 0};
     return 1;
   } else if (B == 4) {
-    out[0] = {P >> 2, hb + 4 * (P & 3), 4, 0};
+    out[0] = {4 * (i >> 2) + r, hb + 4 * (i & 3), 4, 0};
     return 1;
   } else if (B == 8) {
-    out[0] = {P >> 1, hb + 8 * (P & 1), 8, 0};
+    out[0] = {4 * (i >> 1) + r, hb + 8 * (i & 1), 8, 0};
     return 1;
   } else if (B == 3) {
-    const int u = P >> 4, p = P & 15;
-    if (p < 15) {
-      out[0] = {3 * u + p / 5, hb + 3 * (p % 5), 3, 0};
+    // two units of three words; fields at bits 0,3,6,9,12 of each half, bit 15 spare.
+    // k-steps 0-2 take the fields that decode at offset 0 (bits 0 and 9), k-steps 3-5
+    // those at offset 3 (bits 3 and 12), k-steps 6-7 those at offset 6 plus the pair
+    // assembled from the spare bits.
+    if (i < 6) {
+      const int e = 4 * (i % 3) + r;  // 0..11 inside the class
+      const int u = e / 6, f = e % 6;
+      const int q = (i < 3) ? ((f & 1) ? 3 : 0) : ((f & 1) ? 4 : 1);
+      out[0] = {3 * u + (f >> 1), hb + 3 * q, 3, 0};
+      return 1;
+    }
+    const int u = i - 6;
+    if (r < 3) {
+      out[0] = {3 * u + r, hb + 6, 3, 0};
       return 1;
     }
     out[0] = {3 * u + 0, hb + 15, 1, 0};
@@ -94,12 +113,13 @@ template <int B> MG_HD int code_pieces(int P, int h, Piece (&out)[3]) {
     out[2] = {3 * u + 2, hb + 15, 1, 2};
     return 3;
   } else {  // B == 6
-    const int u = P >> 3, p = P & 7;
-    if (p < 6) {
-      out[0] = {3 * u + (p >> 1), hb + 6 * (p & 1), 6, 0};
+    // four units of three words; fields at bits 0 and 6 of each half, bits 12-15 spare
+    const int u = i >> 1, e = 4 * (i & 1) + r;
+    if (e < 6) {
+      out[0] = {3 * u + (e >> 1), hb + 6 * (e & 1), 6, 0};
       return 1;
     }
-    if (p == 6) {
+    if (e == 6) {
       out[0] = {3 * u + 0, hb + 12, 4, 0};
       out[1] = {3 * u + 1, hb + 12, 2, 4};
       return 2;
@@ -108,6 +128,11 @@ template <int B> MG_HD int code_pieces(int P, int h, Piece (&out)[3]) {
     out[1] = {3 * u + 2, hb + 12, 4, 2};
     return 2;
   }
+}
+
+// Bit offset (inside the 10-bit fp16 mantissa) at which the fields of k-step i decode.
+template <int B> MG_HD constexpr int kstep_offset(int i) {
+  return (B == 2) ? 2 * (i % 3) : (B == 4) ? 4 * (i & 1) : (B == 3) ? (i < 3 ? 0 : (i < 6 ? 3 : 6)) : 0;
 }
 
 // Store code c (b bits) as half h of pair P into a lane's words.
