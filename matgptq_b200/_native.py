@@ -8,7 +8,9 @@ from __future__ import annotations
 import ctypes
 import os
 
-_LIB_PATH = os.path.join(os.path.dirname(os.path.abspath(__file__)), "libmatgptq_b200.so")
+# MATGPTQ_B200_LIBRARY points at another build of the same library (for A/B measurements)
+_LIB_PATH = os.environ.get("MATGPTQ_B200_LIBRARY") or os.path.join(
+    os.path.dirname(os.path.abspath(__file__)), "libmatgptq_b200.so")
 
 OK = 0
 FLAG_ASYNC = 1

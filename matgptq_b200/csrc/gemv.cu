@@ -99,11 +99,14 @@ __device__ __forceinline__ uint16_t ldg_u16(const uint16_t *p) {
   return r;
 }
 
-// Blocks per ring stage: about 2 KB of packed weights.
+// Blocks per ring stage (1 to 2 KB of packed weights; the blocks of a stage are decoded
+// interleaved) and ring stages per warp (6 to 8 KB in flight per warp).
 template <int B> struct ChunkBlocks {
-  static constexpr int value = (B == 2) ? 4 : (B == 3 || B == 4) ? 2 : 1;
+  static constexpr int value = (B <= 4) ? 2 : 1;
 };
-constexpr int kStages = 4;   // ring stages per warp
+template <int B> struct Stages {
+  static constexpr int value = (B == 2) ? 6 : (B == 3 || B == 6) ? 5 : 4;
+};
 // blocks (128 in-features each) per activation stage: a multiple of every ChunkBlocks value
 template <int NT> struct XBlocks {
   static constexpr int value = (NT == 1) ? 8 : 4;
@@ -125,13 +128,13 @@ __host__ __device__ inline SmemPlan make_plan(int R, int M, int max_nblk) {
   p.scale_bytes_per_block = (GS == -1) ? 0 : (GS == 32 ? 128 : 32);
   p.stage_bytes = ChunkBlocks<B>::value * (BlockTraits<B>::WORDS * 4 + p.scale_bytes_per_block);
   p.off_bars = 0;
-  p.off_x = 128 * ((8 * (R * kStages + 2) + 127) / 128);
+  p.off_x = 128 * ((8 * (R * Stages<B>::value + 2) + 127) / 128);
   // per activation stage: for every block and group the sum of each activation row (fp32)
   p.sums_per_block = ((GS == 32) ? 4 : 1) * NT * 8;
   p.off_sums = p.off_x + 2 * p.xrows * p.xstride_h * 2;
   p.off_red = p.off_sums + 2 * XBlocks<NT>::value * p.sums_per_block * 4;
   p.off_ring = 128 * ((p.off_red + NT * 8 * p.rstride * 4 + 127) / 128);
-  p.total = p.off_ring + R * kStages * p.stage_bytes;
+  p.total = p.off_ring + R * Stages<B>::value * p.stage_bytes;
   return p;
 }
 
@@ -159,6 +162,7 @@ __global__ void __launch_bounds__(256, 2) gemv_kernel(const GemvParams p) {
   const int groups = (GS == -1) ? 1 : p.K / GS;
 
   constexpr int CB = ChunkBlocks<B>::value;
+  constexpr int kStages = Stages<B>::value;
   constexpr int kXBlocks = XBlocks<NT>::value;
   constexpr int BW = BlockTraits<B>::WORDS;
   constexpr int WBYTES = BW * 4;  // packed bytes per block
@@ -173,8 +177,12 @@ __global__ void __launch_bounds__(256, 2) gemv_kernel(const GemvParams p) {
   const int rstride = plan.rstride;
   const int SCB = plan.scale_bytes_per_block;
 
-  if (threadIdx.x == 0) {
-    for (int i = 0; i < R * kStages + 2; ++i) mbar_init(smem_base + plan.off_bars + i * 8, 1);
+  if (lane == 0) {
+    for (int i = 0; i < kStages; ++i) mbar_init(bar_full0 + i * 8, 1);
+    if (warp == 0) {
+      mbar_init(bar_x0, 1);
+      mbar_init(bar_x0 + 8, 1);
+    }
     mbar_init_fence();
   }
   __syncthreads();
@@ -303,9 +311,7 @@ __global__ void __launch_bounds__(256, 2) gemv_kernel(const GemvParams p) {
         }
         const unsigned char *stage = ring + st * plan.stage_bytes;
         const int nb = min(CB, nblk - c * CB);
-#pragma unroll
-        for (int cb = 0; cb < CB; ++cb) {
-          if (cb < nb) {
+        auto do_block = [&](int cb) {
             const int bi = c * CB + cb - xi * kXBlocks;  // block inside the x stage
             uint32_t w[2 * B];
             {
@@ -400,7 +406,13 @@ __global__ void __launch_bounds__(256, 2) gemv_kernel(const GemvParams p) {
                 yacc[nt][3] = fmaf(shi, tsum[3], yacc[nt][3]);
               }
             }
-          }
+        };
+        if (nb == CB) {
+          // full chunk: no per-block branches, so the blocks' instruction streams can interleave
+#pragma unroll
+          for (int cb = 0; cb < CB; ++cb) do_block(cb);
+        } else {
+          for (int cb = 0; cb < nb; ++cb) do_block(cb);
         }
         // the stage has been read into registers by every lane: refill it
         __syncwarp();
