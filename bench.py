@@ -36,6 +36,9 @@ BATCHES = (1, 2, 4, 8, 16)
 BITS = synth.BITWIDTHS
 GROUP = 128
 ROW_PARALLEL = {"q_o": True, "k_v": False, "gate_up": False, "down": True}
+# dram__bytes_read+write of mg::gemv_kernel divided by its algorithmic bytes, from the ncu capture
+# summarised in profiles/gemv_gate_up_b4_m1_full.md (30.32 MB measured / 30.31 MB algorithmic)
+DRAM_TRAFFIC_PER_ALGORITHMIC_BYTE = 1.0004
 
 
 def measured_peaks() -> tuple[float, str]:
@@ -61,7 +64,7 @@ class ClockSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "100"],
+                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "20"],
                 stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
         except OSError:
             self.proc = None
@@ -264,15 +267,22 @@ def ours_main(args) -> None:
         with torch.cuda.graph(graph, stream=stream):
             for c in cells:
                 launch_cell(c, flags, world)
-        for _ in range(max(args.warmup, 3)):
+        sampler = ClockSampler(local_rank)
+        if rank == 0:
+            sampler.start()
+        # warm-up: at least W replays and at least 0.3 s under load, so that the clocks have
+        # ramped up and nvidia-smi has samples taken under the same load as the timed steps
+        t_warm = time.perf_counter()
+        n_warm = 0
+        while n_warm < max(args.warmup, 3) or time.perf_counter() - t_warm < 0.3:
             graph.replay()
+            n_warm += 1
+            if n_warm % 16 == 0:
+                stream.synchronize()
         stream.synchronize()
         if world > 1:
             torch.distributed.barrier()
         torch.cuda.synchronize()
-        sampler = ClockSampler(local_rank)
-        if rank == 0:
-            sampler.start()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record(stream)
         for _ in range(args.steps):
@@ -319,9 +329,11 @@ def ours_main(args) -> None:
         "clocks": clocks,
         "gpu_launches": launches_per_step * args.steps,
         "roofline": {"bound": "hbm", "achieved": round(value / world, 2), "peak": peak, "unit": "GB/s",
-                     "frac": round(value / world / peak, 4), "traffic": None, "peak_kind": peak_kind,
-                     "kernel": "mg::gemv_kernel (all instantiations of the step)",
-                     "bytes_per_step": step_bytes},
+                     "frac": round(value / world / peak, 4),
+                     "traffic": round(step_bytes / launches_per_step * DRAM_TRAFFIC_PER_ALGORITHMIC_BYTE),
+                     "peak_kind": peak_kind, "kernel": "mg::gemv_kernel (all instantiations of the step)",
+                     "algorithmic_bytes_per_launch": round(step_bytes / launches_per_step),
+                     "mean_launch_us": round(ms_per_step * 1e3 / launches_per_step, 3)},
     }
     if e2e is not None:
         line["e2e"] = e2e
@@ -393,7 +405,7 @@ def main() -> None:
                     help="shape:b:m, e.g. q_o:4:1 - only launch this cell (--launches times) and exit")
     ap.add_argument("--launches", type=int, default=8)
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--no-pdl", action="store_true", help="launch without programmatic dependent launch")

@@ -61,6 +61,25 @@ int matgptq_b200_matmul_tuned(int64_t bitwidth, int64_t group_size, int64_t n_ou
                               int warps_per_cta, int split_k);
 
 /*
+ * The same product with caller-provided scratch memory.  Batches of 32 rows and more run
+ * on the tensor cores (tcgen05); for shapes with few 128-row tiles that path splits K over
+ * several CTAs and needs matgptq_b200_matmul_workspace_bytes(...) bytes of device scratch
+ * (16-byte aligned; contents undefined before and after; one buffer per stream in flight).
+ * Without scratch (workspace NULL, or matgptq_b200_matmul) K is not split.
+ *   path: 0 = choose by batch size, 1 = GEMV family, 2 = tensor-core path (any batch size)
+ *   split_k: 0 = choose; otherwise the number of CTAs along K (tensor-core path: needs
+ *            split_k*M*N*4 bytes of scratch)
+ * The reference has one kernel pair for all batch sizes and no scratch
+ * (csrc/matgptq_gemm.cu:955-964); this entry has no counterpart there.
+ */
+int matgptq_b200_matmul_ws(int64_t bitwidth, int64_t group_size, int64_t n_out, int64_t n_in, int64_t batch,
+                           const void *w, const void *s, const void *x, void *y, void *stream, uint32_t flags,
+                           void *workspace, int64_t workspace_bytes, int path, int split_k);
+
+/* Scratch bytes matgptq_b200_matmul_ws wants for this shape on the current device (0 = none). */
+int64_t matgptq_b200_matmul_workspace_bytes(int64_t n_out, int64_t n_in, int64_t batch);
+
+/*
  * MSB slicing of 8-bit master codes to b bits with round-to-nearest and saturation.
  * Replaces matryoshka_slice (src/quant_utils_matgpqt.py:9-17).  In and out are
  * device buffers of numel bytes and may be the same buffer.

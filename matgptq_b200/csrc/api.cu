@@ -40,22 +40,40 @@ const char *matgptq_b200_strerror(int status) {
   }
 }
 
-int matgptq_b200_matmul_tuned(int64_t bitwidth, int64_t group_size, int64_t n_out, int64_t n_in, int64_t batch,
-                              const void *w, const void *s, const void *x, void *y, void *stream, uint32_t flags,
-                              int warps_per_cta, int split_k) {
+// Batches from this size on take the tensor-core path (tcgen05), smaller ones the GEMV family.
+static const int64_t kTensorCoreMinBatch = 32;
+
+static int sm_count_of_current_device(int *out) {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return MG_ERR_CUDA;
+  if (cudaDeviceGetAttribute(out, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return MG_ERR_CUDA;
+  return MG_OK;
+}
+
+static int matmul_impl(int64_t bitwidth, int64_t group_size, int64_t n_out, int64_t n_in, int64_t batch, const void *w,
+                       const void *s, const void *x, void *y, void *stream, uint32_t flags, void *workspace,
+                       int64_t workspace_bytes, int path, int warps_per_cta, int split_k) {
   const int st = check_shape(n_out, n_in, bitwidth, group_size);
   if (st != MG_OK) return st;
-  if (batch < 0 || batch > (1 << 24)) return MG_ERR_BAD_ARG;
+  if (batch < 0 || batch > (1 << 24) || path < 0 || path > 2 || workspace_bytes < 0) return MG_ERR_BAD_ARG;
   if (batch == 0) return MG_OK;
   if (!w || !s || !x || !y) return MG_ERR_BAD_ARG;
-  if (!aligned16(w) || !aligned16(x) || !aligned16(s) || (reinterpret_cast<uintptr_t>(y) & 1u))
+  if (!aligned16(w) || !aligned16(x) || !aligned16(s) || (reinterpret_cast<uintptr_t>(y) & 1u) ||
+      (workspace && !aligned16(workspace)))
     return MG_ERR_ALIGNMENT;
   cudaStream_t cs = static_cast<cudaStream_t>(stream);
   const bool bf16 = (flags & MATGPTQ_B200_FLAG_BF16) != 0;
   const bool pdl = (flags & MATGPTQ_B200_FLAG_PDL) != 0;
-  const int r = mg::gemv_launch(static_cast<int>(bitwidth), static_cast<int>(group_size), static_cast<int>(n_out),
-                                static_cast<int>(n_in), static_cast<int>(batch), w, s, x, y, bf16, pdl, warps_per_cta,
-                                split_k, cs);
+  const bool tensor_core = path == 2 || (path == 0 && batch >= kTensorCoreMinBatch);
+  int r;
+  if (tensor_core) {
+    r = mg::gemm_tc_launch(static_cast<int>(bitwidth), static_cast<int>(group_size), static_cast<int>(n_out),
+                           static_cast<int>(n_in), static_cast<int>(batch), w, s, x, y, workspace, workspace_bytes, bf16,
+                           pdl, split_k, cs);
+  } else {
+    r = mg::gemv_launch(static_cast<int>(bitwidth), static_cast<int>(group_size), static_cast<int>(n_out),
+                        static_cast<int>(n_in), static_cast<int>(batch), w, s, x, y, bf16, pdl, warps_per_cta, split_k, cs);
+  }
   if (r != MG_OK) return r;
   if (!(flags & MATGPTQ_B200_FLAG_ASYNC)) {
     // the reference synchronises the whole device in this mode (csrc/matgptq_gemm.cu:1060-1062)
@@ -64,9 +82,30 @@ int matgptq_b200_matmul_tuned(int64_t bitwidth, int64_t group_size, int64_t n_ou
   return MG_OK;
 }
 
+int matgptq_b200_matmul_tuned(int64_t bitwidth, int64_t group_size, int64_t n_out, int64_t n_in, int64_t batch,
+                              const void *w, const void *s, const void *x, void *y, void *stream, uint32_t flags,
+                              int warps_per_cta, int split_k) {
+  return matmul_impl(bitwidth, group_size, n_out, n_in, batch, w, s, x, y, stream, flags, nullptr, 0, 1, warps_per_cta,
+                     split_k);
+}
+
 int matgptq_b200_matmul(int64_t bitwidth, int64_t group_size, int64_t n_out, int64_t n_in, int64_t batch,
                         const void *w, const void *s, const void *x, void *y, void *stream, uint32_t flags) {
-  return matgptq_b200_matmul_tuned(bitwidth, group_size, n_out, n_in, batch, w, s, x, y, stream, flags, 0, 0);
+  return matmul_impl(bitwidth, group_size, n_out, n_in, batch, w, s, x, y, stream, flags, nullptr, 0, 0, 0, 0);
+}
+
+int matgptq_b200_matmul_ws(int64_t bitwidth, int64_t group_size, int64_t n_out, int64_t n_in, int64_t batch,
+                           const void *w, const void *s, const void *x, void *y, void *stream, uint32_t flags,
+                           void *workspace, int64_t workspace_bytes, int path, int split_k) {
+  return matmul_impl(bitwidth, group_size, n_out, n_in, batch, w, s, x, y, stream, flags, workspace, workspace_bytes, path,
+                     0, split_k);
+}
+
+int64_t matgptq_b200_matmul_workspace_bytes(int64_t n_out, int64_t n_in, int64_t batch) {
+  if (n_out <= 0 || n_in <= 0 || batch < kTensorCoreMinBatch) return 0;
+  int sms = 0;
+  if (sm_count_of_current_device(&sms) != MG_OK) sms = 148;
+  return mg::gemm_tc_workspace_bytes(static_cast<int>(n_out), static_cast<int>(n_in), static_cast<int>(batch), sms);
 }
 
 int matgptq_b200_slice(const uint8_t *master_codes, uint8_t *sliced_codes, int64_t numel, int master_bitwidth,
@@ -137,7 +176,13 @@ int matgptq_b200_dequantize(const uint32_t *packed, const void *scales, const vo
 
 int matgptq_b200_device_status(int *status_out, int reset) {
   if (cudaDeviceSynchronize() != cudaSuccess) return MG_ERR_CUDA;
-  return mg::gemv_device_status(status_out, reset);
+  int a = 0, b = 0;
+  int r = mg::gemv_device_status(&a, reset);
+  if (r != MG_OK) return r;
+  r = mg::gemm_tc_device_status(&b, reset);
+  if (r != MG_OK) return r;
+  if (status_out) *status_out = a ? a : b;
+  return MG_OK;
 }
 
 }  // extern "C"

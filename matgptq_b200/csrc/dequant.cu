@@ -14,37 +14,6 @@
 
 namespace mg {
 
-template <bool BF16> __device__ __forceinline__ uint32_t splat16(uint16_t v) {
-  return static_cast<uint32_t>(v) | (static_cast<uint32_t>(v) << 16);
-}
-
-// v: pair of exact integers (code - Z) as half2.  Returns the dequantised pair in the output dtype.
-template <int B, bool BF16>
-__device__ __forceinline__ uint32_t dequant_pair(uint32_t v, uint16_t scale, bool has_zero, uint16_t zero) {
-  constexpr float kShift = static_cast<float>(1 << (8 - B));
-  if constexpr (BF16) {
-    const uint32_t vb = h2_to_bf2(v);
-    const __nv_bfloat162 vi = *reinterpret_cast<const __nv_bfloat162 *>(&vb);
-    const __nv_bfloat162 sh = __float2bfloat162_rn(kShift);
-    __nv_bfloat162 off = __float2bfloat162_rn(0.f);
-    if (has_zero) {
-      const uint32_t zb = splat16<BF16>(zero);
-      off = __hsub2(__float2bfloat162_rn(128.f), *reinterpret_cast<const __nv_bfloat162 *>(&zb));
-    }
-    const __nv_bfloat162 q = __hfma2(vi, sh, off);  // exact integer
-    const uint32_t sb = splat16<BF16>(scale);
-    const __nv_bfloat162 r = __hmul2(*reinterpret_cast<const __nv_bfloat162 *>(&sb), q);
-    return *reinterpret_cast<const uint32_t *>(&r);
-  } else {
-    const __half2 vi = bits_h2(v);
-    const __half2 sh = __float2half2_rn(kShift);
-    __half2 off = __float2half2_rn(0.f);
-    if (has_zero) off = __hsub2(__float2half2_rn(128.f), bits_h2(splat16<BF16>(zero)));
-    const __half2 q = __hfma2(vi, sh, off);  // exact integer
-    return h2_bits(__hmul2(bits_h2(splat16<BF16>(scale)), q));
-  }
-}
-
 template <int B, int GS, bool BF16>
 __global__ void __launch_bounds__(256) dequant_kernel(const uint32_t *__restrict__ packed, const uint16_t *__restrict__ scales,
                                                       const uint16_t *__restrict__ zeros, uint16_t *__restrict__ w_out, int tiles,

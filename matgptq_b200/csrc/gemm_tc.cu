@@ -1,0 +1,458 @@
+// Tensor-core path for batches of 32 rows and more: tcgen05.mma with the accumulator
+// in tensor memory.
+//
+// Replaces gptq_matryoshka for large batches (csrc/matgptq_gemm.cu:337-634), which
+// re-reads the weights once per 8 batch columns and stays below a dense fp16 GEMM
+// from M = 32 up.  Here one CTA owns 128 out-features and up to 256 batch rows:
+//
+//   * eight "dequant" warps (one per 16-row tile of the packed layout) decode their
+//     block to the exact dense weights of the reference's dequantize()
+//     (round(scale * (code*2^(8-b) - 128)), fp16 or bf16) and store them K-major into a
+//     shared-memory stage in the canonical no-swizzle UMMA layout (8 x 16-byte core
+//     matrices); the same warps copy the activation tile into the 128-byte-swizzled
+//     K-major layout with cp.async;
+//   * a ninth warp issues tcgen05.mma (M = 128 weights rows, N = batch rows, K = 16)
+//     from shared-memory descriptors; D[128, N] lives in tensor memory; completion
+//     of a stage's MMAs releases the stage through tcgen05.commit -> mbarrier;
+//   * the epilogue reads D with tcgen05.ld (each warp its own 32 TMEM lanes), converts
+//     and stores y[m, n] (the transpose of D), or, when K is split over several CTAs,
+//     stores fp32 partial sums into caller-provided scratch memory that a second small
+//     kernel adds up in a fixed order.
+//
+// Every mbarrier wait is bounded (async.cuh); tensor memory is freed on every path.
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include "async.cuh"
+#include "decode.cuh"
+#include "kernels.h"
+
+namespace mg {
+
+// A pipeline stage covers 64 in-features (half a packed block).
+constexpr int kTcChunkStride = 2080;   // bytes between 16-byte K chunks of the A stage: 128 rows * 16 B + 32 B
+                                       // (the 32 bytes spread the four k-chunks a warp stores at once over all banks)
+constexpr int kTcAStageBytes = 8 * kTcChunkStride;  // 8 chunks of 8 in-features
+constexpr int kTcThreads = 9 * 32;
+
+struct GemmParams {
+  const uint32_t *w;
+  const uint16_t *s;
+  const uint16_t *x;
+  uint16_t *y;
+  float *partial;  // [split][M][N] fp32 when split > 1
+  int N, K, M;
+  int kblocks;  // K / 128
+  int split;    // CTAs along K
+  int ncols;    // UMMA N: batch rows per pass rounded up to 16
+  int stages;
+};
+
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void *src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+
+// 64-bit shared-memory matrix descriptor (K-major).  layout_type: 0 = no swizzle, 2 = 128-byte swizzle.
+__device__ __forceinline__ uint64_t umma_smem_desc(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes, uint32_t layout_type) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((addr >> 4) & 0x3FFFu);
+  d |= static_cast<uint64_t>((lbo_bytes >> 4) & 0x3FFFu) << 16;
+  d |= static_cast<uint64_t>((sbo_bytes >> 4) & 0x3FFFu) << 32;
+  d |= 1ull << 46;  // descriptor version of this architecture
+  d |= static_cast<uint64_t>(layout_type & 7u) << 61;
+  return d;
+}
+
+// 32-bit instruction descriptor: fp32 accumulate, A and B both K-major, both fp16 (0) or bf16 (1).
+__host__ __device__ inline uint32_t umma_instr_desc(int fmt, int n) {
+  return (1u << 4) | (static_cast<uint32_t>(fmt) << 7) | (static_cast<uint32_t>(fmt) << 10) |
+         (static_cast<uint32_t>(n >> 3) << 17) | (static_cast<uint32_t>(128 >> 4) << 24);
+}
+
+__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n"
+      "  .reg .pred p;\n"
+      "  setp.ne.b32 p, %4, 0;\n"
+      "  tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n"
+      "}\n" ::"r"(tmem_d),
+      "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+        "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]),
+        "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]),
+        "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+      : "r"(taddr));
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// shared-memory plan (host and device)
+struct TcPlan {
+  int b_stage_bytes, stage_bytes, off_stages, total;
+};
+__host__ __device__ inline TcPlan tc_plan(int ncols, int stages) {
+  TcPlan p;
+  p.b_stage_bytes = ncols * 128;                               // 64 in-features * 2 B per batch row
+  p.stage_bytes = 1024 * ((kTcAStageBytes + p.b_stage_bytes + 1023) / 1024);  // B first, 1024-aligned for the swizzle
+  p.off_stages = 1024;                                         // barriers and the TMEM address live below
+  p.total = p.off_stages + stages * p.stage_bytes + 1024;      // slack to align the dynamic base to 1024
+  return p;
+}
+
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&v)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+        "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
+      : "r"(taddr));
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// scales of one block for a lane's rows g and g+8 (NG groups per block)
+template <int GS> struct TcScales {
+  static constexpr int NG = (GS == 32) ? 4 : 1;
+  uint16_t lo[NG], hi[NG];
+};
+
+template <int GS>
+__device__ __forceinline__ void tc_load_scales(const uint16_t *s, int tile16, int kb, int groups, int g, TcScales<GS> &r) {
+  constexpr int NG = TcScales<GS>::NG;
+  const int grp0 = (GS == -1) ? 0 : kb * NG;
+  const uint16_t *base = s + (static_cast<size_t>(tile16) * groups + grp0) * 16 + g;
+#pragma unroll
+  for (int j = 0; j < NG; ++j) {
+    r.lo[j] = __ldg(base + j * 16);
+    r.hi[j] = __ldg(base + j * 16 + 8);
+  }
+}
+
+template <int B, int GS, bool BF16>
+__global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const GemmParams p) {
+  extern __shared__ unsigned char tc_smem_raw[];
+  const uint32_t raw_u32 = smem_u32(tc_smem_raw);
+  const uint32_t base_u32 = (raw_u32 + 1023u) & ~1023u;
+  unsigned char *base = tc_smem_raw + (base_u32 - raw_u32);
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int g = lane >> 2, t = lane & 3;
+  const int stages = p.stages;
+  const TcPlan plan = tc_plan(p.ncols, stages);
+  const uint32_t bar_full = base_u32;               // stages barriers, 8 arrivals each
+  const uint32_t bar_empty = base_u32 + 8 * 8;      // stages barriers, released by tcgen05.commit
+  const uint32_t bar_done = base_u32 + 16 * 8;
+  volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(base + 17 * 8);
+
+  const int tile128 = blockIdx.x, sk = blockIdx.y;
+  const int m0 = blockIdx.z * 256;
+  const int mrows = min(p.M - m0, 256);
+  const int kb_lo = static_cast<int>(static_cast<long long>(sk) * p.kblocks / p.split);
+  const int kb_hi = static_cast<int>(static_cast<long long>(sk + 1) * p.kblocks / p.split);
+  const int nblk = kb_hi - kb_lo;
+  const int nit = 2 * nblk;  // pipeline iterations of 64 in-features
+  const int groups = (GS == -1) ? 1 : p.K / GS;
+  int tmem_cols = 32;
+  while (tmem_cols < p.ncols) tmem_cols <<= 1;
+
+  if (warp == 8) {
+    if (lane == 0) {
+      for (int i = 0; i < stages; ++i) {
+        mbar_init(bar_full + i * 8, 8);
+        mbar_init(bar_empty + i * 8, 1);
+      }
+      mbar_init(bar_done, 1);
+      mbar_init_fence();
+    }
+    __syncwarp();
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(base_u32 + 17 * 8), "r"(tmem_cols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem_base = *tmem_slot;
+
+  // The activations may come from the kernel launched just before this one.
+  asm volatile("griddepcontrol.launch_dependents;");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+
+  bool failed = false;
+  if (warp < 8) {
+    // ------------------------------------------------------------------ producers
+    const int tile16 = tile128 * 8 + warp;
+    const bool valid = tile16 < p.N / 16;
+    constexpr int BW = BlockTraits<B>::WORDS;
+    const uint32_t *wsrc = p.w + (static_cast<size_t>(valid ? tile16 : 0) * p.kblocks + kb_lo) * BW;
+    uint32_t w[2 * B], wn[2 * B];
+    TcScales<GS> sc, scn;
+    if (valid) {
+      load_block<B>(wsrc, lane, wn);
+      tc_load_scales<GS>(p.s, tile16, kb_lo, groups, g, scn);
+    }
+    for (int it = 0; it < nit && !failed; ++it) {
+      const int s = it % stages;
+      if (!mbar_wait(bar_empty + s * 8, ((it / stages) & 1) ^ 1)) {
+        failed = true;
+        report_status(kStatusMmaTimeout);
+        break;
+      }
+      const uint32_t stage_b = base_u32 + plan.off_stages + s * plan.stage_bytes;
+      const uint32_t stage_a = stage_b + plan.b_stage_bytes;
+      const int h = it & 1, kbl = it >> 1;
+      // activation tile: row r, 16-byte chunk c of the 64 in-features, 128-byte swizzle
+      {
+        const uint16_t *xsrc = p.x + static_cast<size_t>(m0) * p.K + static_cast<size_t>(kb_lo + kbl) * 128 + h * 64;
+        for (int idx = tid; idx < mrows * 8; idx += 256) {
+          const int r = idx >> 3, c = idx & 7;
+          cp_async16(stage_b + r * 128 + ((c ^ (r & 7)) << 4), xsrc + static_cast<size_t>(r) * p.K + c * 8);
+        }
+      }
+      if (h == 0) {
+#pragma unroll
+        for (int j = 0; j < 2 * B; ++j) w[j] = wn[j];
+        sc = scn;
+        if (valid && kbl + 1 < nblk) {
+          load_block<B>(wsrc + static_cast<size_t>(kbl + 1) * BW, lane, wn);
+          tc_load_scales<GS>(p.s, tile16, kb_lo + kbl + 1, groups, g, scn);
+        }
+      }
+      if (valid) {
+        // dense weights of this lane: rows g and g+8, two 16-byte chunks per row
+        auto emit = [&](int jj) {
+          const int gi = (GS == 32) ? jj : 0;
+          uint4 lo, hi;
+          lo.x = dequant_pair<B, BF16>(decode_pair<B>(w, 8 * jj + 0), sc.lo[gi], false, 0);
+          lo.y = dequant_pair<B, BF16>(decode_pair<B>(w, 8 * jj + 2), sc.lo[gi], false, 0);
+          lo.z = dequant_pair<B, BF16>(decode_pair<B>(w, 8 * jj + 4), sc.lo[gi], false, 0);
+          lo.w = dequant_pair<B, BF16>(decode_pair<B>(w, 8 * jj + 6), sc.lo[gi], false, 0);
+          hi.x = dequant_pair<B, BF16>(decode_pair<B>(w, 8 * jj + 1), sc.hi[gi], false, 0);
+          hi.y = dequant_pair<B, BF16>(decode_pair<B>(w, 8 * jj + 3), sc.hi[gi], false, 0);
+          hi.z = dequant_pair<B, BF16>(decode_pair<B>(w, 8 * jj + 5), sc.hi[gi], false, 0);
+          hi.w = dequant_pair<B, BF16>(decode_pair<B>(w, 8 * jj + 7), sc.hi[gi], false, 0);
+          const int chunk = 4 * (jj & 1) + t;
+          unsigned char *dst = base + plan.off_stages + s * plan.stage_bytes + plan.b_stage_bytes +
+                               chunk * kTcChunkStride + (2 * warp) * 128 + g * 16;
+          *reinterpret_cast<uint4 *>(dst) = lo;
+          *reinterpret_cast<uint4 *>(dst + 128) = hi;
+        };
+        if (h == 0) {
+          emit(0);
+          emit(1);
+        } else {
+          emit(2);
+          emit(3);
+        }
+      }
+      asm volatile("cp.async.wait_all;" ::: "memory");
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_full + s * 8);
+      (void)stage_a;
+    }
+  } else if (lane == 0) {
+    // ------------------------------------------------------------------ MMA issuer
+    const uint32_t idesc = umma_instr_desc(BF16 ? 1 : 0, p.ncols);
+    for (int it = 0; it < nit && !failed; ++it) {
+      const int s = it % stages;
+      if (!mbar_wait(bar_full + s * 8, (it / stages) & 1)) {
+        failed = true;
+        report_status(kStatusWeightCopyTimeout);
+        break;
+      }
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const uint32_t stage_b = base_u32 + plan.off_stages + s * plan.stage_bytes;
+      const uint32_t stage_a = stage_b + plan.b_stage_bytes;
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const uint64_t da = umma_smem_desc(stage_a + 2 * k * kTcChunkStride, kTcChunkStride, 128, 0);
+        const uint64_t db = umma_smem_desc(stage_b + k * 32, 16, 1024, 2);
+        umma_f16(tmem_base, da, db, idesc, (it > 0 || k > 0) ? 1u : 0u);
+      }
+      umma_commit(bar_empty + s * 8);
+    }
+    if (!failed) umma_commit(bar_done);
+  }
+
+  // ---------------------------------------------------------------------- epilogue
+  if (warp < 8 && !failed) {
+    if (!mbar_wait(bar_done, 0)) {
+      failed = true;
+      report_status(kStatusMmaTimeout);
+    }
+  }
+  if (warp < 8 && !failed) {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const int q = warp & 3;
+    const int n = tile128 * 128 + q * 32 + lane;
+    const int nchunks = p.ncols / 16;
+    for (int ci = (warp >> 2); ci < nchunks; ci += 2) {
+      uint32_t v[16];
+      tmem_ld16(tmem_base + (static_cast<uint32_t>(q * 32) << 16) + ci * 16, v);
+      if (n < p.N) {
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          const int m = m0 + ci * 16 + j;
+          if (m < m0 + mrows) {
+            const float f = __uint_as_float(v[j]);
+            if (p.split > 1) {
+              p.partial[(static_cast<size_t>(sk) * p.M + m) * p.N + n] = f;
+            } else if (BF16) {
+              p.y[static_cast<size_t>(m) * p.N + n] = __bfloat16_as_ushort(__float2bfloat16_rn(f));
+            } else {
+              p.y[static_cast<size_t>(m) * p.N + n] = __half_as_ushort(__float2half_rn(f));
+            }
+          }
+        }
+      }
+    }
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == 8) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(tmem_cols) : "memory");
+  }
+}
+
+// partial[split][M][N] fp32 -> y[M][N], added in a fixed order
+template <bool BF16>
+__global__ void splitk_reduce_kernel(const float *__restrict__ partial, uint16_t *__restrict__ y, long long mn, int split) {
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < mn;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    float sum = 0.f;
+    for (int s = 0; s < split; ++s) sum += partial[static_cast<long long>(s) * mn + i];
+    y[i] = BF16 ? __bfloat16_as_ushort(__float2bfloat16_rn(sum)) : __half_as_ushort(__float2half_rn(sum));
+  }
+}
+
+// ----------------------------------------------------------------------------
+// host side
+// ----------------------------------------------------------------------------
+static int round_up16(int v) { return (v + 15) / 16 * 16; }
+
+// K split of the tensor-core path: enough CTAs to cover the SMs, at least two blocks each.
+int gemm_tc_pick_split(int N, int K, int M, int sm_count) {
+  const int ctas = ((N + 127) / 128) * ((M + 255) / 256);
+  const int kblocks = K / 128;
+  int split = 1;
+  while (split < 8 && ctas * split * 2 <= sm_count + sm_count / 4 && kblocks / (split * 2) >= 2) split *= 2;
+  return split;
+}
+
+long long gemm_tc_workspace_bytes(int N, int K, int M, int sm_count) {
+  const int split = gemm_tc_pick_split(N, K, M, sm_count);
+  return split > 1 ? static_cast<long long>(split) * M * N * 4 : 0;
+}
+
+template <int B, int GS, bool BF16>
+static int launch_gemm_tc(GemmParams p, cudaStream_t stream, bool pdl) {
+  auto kernel = gemm_tc_kernel<B, GS, BF16>;
+  p.ncols = round_up16(p.M < 256 ? p.M : 256);
+  int stages = 4;
+  while (stages > 2 && tc_plan(p.ncols, stages).total > 200 * 1024) --stages;
+  p.stages = stages;
+  const TcPlan plan = tc_plan(p.ncols, stages);
+  static bool opted_in[64] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return MG_ERR_CUDA;
+  if (dev < 0 || dev >= 64) return MG_ERR_BAD_ARG;
+  if (!opted_in[dev]) {
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) != cudaSuccess) return MG_ERR_CUDA;
+    opted_in[dev] = true;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((p.N + 127) / 128, p.split, (p.M + 255) / 256);
+  cfg.blockDim = dim3(kTcThreads, 1, 1);
+  cfg.dynamicSmemBytes = plan.total;
+  cfg.stream = stream;
+  cudaLaunchAttribute attrs[1];
+  int na = 0;
+  if (pdl) {
+    attrs[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attrs[na].val.programmaticStreamSerializationAllowed = 1;
+    ++na;
+  }
+  cfg.attrs = attrs;
+  cfg.numAttrs = na;
+  if (cudaLaunchKernelEx(&cfg, kernel, p) != cudaSuccess) return MG_ERR_CUDA;
+  if (p.split > 1) {
+    const long long mn = static_cast<long long>(p.M) * p.N;
+    long long blocks = (mn + 255) / 256;
+    if (blocks > 148 * 8) blocks = 148 * 8;
+    splitk_reduce_kernel<BF16><<<static_cast<unsigned>(blocks), 256, 0, stream>>>(p.partial, p.y, mn, p.split);
+    if (cudaGetLastError() != cudaSuccess) return MG_ERR_CUDA;
+  }
+  return MG_OK;
+}
+
+template <int B, int GS>
+static int launch_gemm_tc_type(const GemmParams &p, bool bf16, cudaStream_t stream, bool pdl) {
+  if (bf16) return launch_gemm_tc<B, GS, true>(p, stream, pdl);
+  return launch_gemm_tc<B, GS, false>(p, stream, pdl);
+}
+
+template <int B>
+static int launch_gemm_tc_group(const GemmParams &p, int group_size, bool bf16, cudaStream_t stream, bool pdl) {
+  switch (group_size) {
+    case -1: return launch_gemm_tc_type<B, -1>(p, bf16, stream, pdl);
+    case 32: return launch_gemm_tc_type<B, 32>(p, bf16, stream, pdl);
+    case 128: return launch_gemm_tc_type<B, 128>(p, bf16, stream, pdl);
+    default: return MG_ERR_BAD_ARG;
+  }
+}
+
+// workspace: fp32 scratch of at least gemm_tc_workspace_bytes(), or null to run without a K split
+int gemm_tc_launch(int bitwidth, int group_size, int N, int K, int M, const void *w, const void *s, const void *x,
+                   void *y, void *workspace, long long workspace_bytes, bool bf16, bool pdl, int split_override,
+                   cudaStream_t stream) {
+  static int sm_count = 0;
+  if (sm_count == 0) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return MG_ERR_CUDA;
+    if (cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return MG_ERR_CUDA;
+  }
+  GemmParams p;
+  p.w = static_cast<const uint32_t *>(w);
+  p.s = static_cast<const uint16_t *>(s);
+  p.x = static_cast<const uint16_t *>(x);
+  p.y = static_cast<uint16_t *>(y);
+  p.partial = static_cast<float *>(workspace);
+  p.N = N;
+  p.K = K;
+  p.M = M;
+  p.kblocks = K / 128;
+  int split = split_override > 0 ? split_override : gemm_tc_pick_split(N, K, M, sm_count);
+  if (split > p.kblocks) split = p.kblocks;
+  if (split > 1 && (workspace == nullptr || workspace_bytes < static_cast<long long>(split) * M * N * 4)) {
+    if (split_override > 0) return MG_ERR_BAD_ARG;
+    split = 1;  // no scratch given: every CTA runs the whole K range
+  }
+  p.split = split;
+  p.ncols = 0;
+  p.stages = 0;
+  switch (bitwidth) {
+    case 2: return launch_gemm_tc_group<2>(p, group_size, bf16, stream, pdl);
+    case 3: return launch_gemm_tc_group<3>(p, group_size, bf16, stream, pdl);
+    case 4: return launch_gemm_tc_group<4>(p, group_size, bf16, stream, pdl);
+    case 6: return launch_gemm_tc_group<6>(p, group_size, bf16, stream, pdl);
+    case 8: return launch_gemm_tc_group<8>(p, group_size, bf16, stream, pdl);
+    default: return MG_ERR_BAD_ARG;
+  }
+}
+
+MG_DEFINE_STATUS_ACCESSOR(gemm_tc_device_status)
+
+}  // namespace mg

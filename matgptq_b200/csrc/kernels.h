@@ -20,6 +20,14 @@ int gemv_launch(int bitwidth, int group_size, int N, int K, int M, const void *w
 
 int gemv_device_status(int *status_out, int reset);
 
+// gemm_tc.cu
+int gemm_tc_pick_split(int N, int K, int M, int sm_count);
+long long gemm_tc_workspace_bytes(int N, int K, int M, int sm_count);
+int gemm_tc_launch(int bitwidth, int group_size, int N, int K, int M, const void *w, const void *s, const void *x,
+                   void *y, void *workspace, long long workspace_bytes, bool bf16, bool pdl, int split_override,
+                   cudaStream_t stream);
+int gemm_tc_device_status(int *status_out, int reset);
+
 // pack.cu
 int slice_launch(const uint8_t *in, uint8_t *out, long long numel, int master_bitwidth, int bitwidth,
                  cudaStream_t stream);

@@ -191,9 +191,12 @@ def matmul_matgptq(
         x = x.clone()
     with torch.cuda.device(dev):
         out = torch.empty((batch, n_out_features), dtype=dtype, device=dev)
-        st = _lib.matgptq_b200_matmul(bitwidth, group_size, n_out_features, n_in_features, batch,
-                                      matgptq_weights.data_ptr(), matgptq_scales.data_ptr(), x.data_ptr(),
-                                      out.data_ptr(), _stream_ptr(dev), feature_flag)
+        ws_bytes = _lib.matgptq_b200_matmul_workspace_bytes(n_out_features, n_in_features, batch)
+        ws = torch.empty(ws_bytes, dtype=torch.uint8, device=dev) if ws_bytes > 0 else None
+        st = _lib.matgptq_b200_matmul_ws(bitwidth, group_size, n_out_features, n_in_features, batch,
+                                         matgptq_weights.data_ptr(), matgptq_scales.data_ptr(), x.data_ptr(),
+                                         out.data_ptr(), _stream_ptr(dev), feature_flag,
+                                         ws.data_ptr() if ws is not None else None, ws_bytes, 0, 0)
         _native.check(st, "matmul_matgptq")
     return out
 
@@ -239,14 +242,28 @@ def _dequant_fake(matgptq_weights, matgptq_scales, n_out_features, n_in_features
 
 def matmul_matgptq_raw(x: torch.Tensor, packed: torch.Tensor, scales: torch.Tensor, n_out: int, n_in: int,
                        bitwidth: int, group_size: int, flags: int, out: torch.Tensor | None = None,
-                       warps_per_cta: int = 0, split_k: int = 0) -> torch.Tensor:
+                       warps_per_cta: int = 0, split_k: int = 0, path: int = 0,
+                       workspace: torch.Tensor | None = None) -> torch.Tensor:
     """The C-ABI matmul without the dispatcher around it: no argument checks beyond the library's own,
-    optional preallocated output and forced launch shape.  Used by the decode loop and the benchmarks."""
+    optional preallocated output and scratch, forced path (1 GEMV, 2 tensor cores) and launch shape.
+    Used by the decode loop, the benchmarks and the tests."""
     batch = x.size(-2)
     if out is None:
         out = torch.empty((batch, n_out), dtype=x.dtype, device=x.device)
-    st = _lib.matgptq_b200_matmul_tuned(bitwidth, group_size, n_out, n_in, batch, packed.data_ptr(),
-                                        scales.data_ptr(), x.data_ptr(), out.data_ptr(),
-                                        torch.cuda.current_stream(x.device).cuda_stream, flags, warps_per_cta, split_k)
+    stream = torch.cuda.current_stream(x.device).cuda_stream
+    if warps_per_cta:
+        st = _lib.matgptq_b200_matmul_tuned(bitwidth, group_size, n_out, n_in, batch, packed.data_ptr(),
+                                            scales.data_ptr(), x.data_ptr(), out.data_ptr(), stream, flags,
+                                            warps_per_cta, split_k)
+    else:
+        tensor_core = path == 2 or (path == 0 and batch >= 32)
+        if workspace is None and tensor_core:
+            need = split_k * batch * n_out * 4 if split_k > 1 else _lib.matgptq_b200_matmul_workspace_bytes(n_out, n_in, batch)
+            if need > 0:
+                workspace = torch.empty(need, dtype=torch.uint8, device=x.device)
+        st = _lib.matgptq_b200_matmul_ws(bitwidth, group_size, n_out, n_in, batch, packed.data_ptr(),
+                                         scales.data_ptr(), x.data_ptr(), out.data_ptr(), stream, flags,
+                                         workspace.data_ptr() if workspace is not None else None,
+                                         workspace.numel() if workspace is not None else 0, path, split_k)
     _native.check(st, "matgptq_b200_matmul")
     return out
