@@ -28,6 +28,7 @@ extern "C" {
 #define MATGPTQ_B200_ERR_CUDA 2        /* a CUDA runtime call or a kernel launch failed */
 #define MATGPTQ_B200_ERR_UNSUPPORTED 3 /* valid in the reference but not provided here */
 #define MATGPTQ_B200_ERR_ALIGNMENT 4   /* a pointer is not 16-byte aligned */
+#define MATGPTQ_B200_ERR_SCRATCH_TOO_SMALL 5 /* the shape needs more scratch than the built-in array holds */
 
 /* feature flags: bits 0 and 1 are the reference's (csrc/include/common.cuh:78-86,
  * matgptq_cuda/matgptq_linear.py:6-9); bit 2 is an addition. */
@@ -78,6 +79,29 @@ int matgptq_b200_matmul_ws(int64_t bitwidth, int64_t group_size, int64_t n_out, 
 
 /* Scratch bytes matgptq_b200_matmul_ws wants for this shape on the current device (0 = none). */
 int64_t matgptq_b200_matmul_workspace_bytes(int64_t n_out, int64_t n_in, int64_t batch);
+
+/*
+ * matgptq_b200_matmul_ws for callers that cannot allocate: hosts whose memory pool already
+ * owns the whole device, plugins without access to their host's allocator, loops in which
+ * cudaMalloc is forbidden because it synchronises the device.  The split-K scratch is a fixed
+ * array of MATGPTQ_B200_STATIC_SCRATCH_BYTES inside the library image; it occupies that much
+ * memory on every GPU that loads the library until the process exits.  This entry point has no
+ * counterpart in the reference.
+ *   - It calls no cudaMalloc, cudaFree or any other allocating routine.
+ *   - Shapes whose scratch need (matgptq_b200_matmul_workspace_bytes) exceeds the array return
+ *     MATGPTQ_B200_ERR_SCRATCH_TOO_SMALL and launch nothing.
+ *   - The first call on a device that needs scratch resolves the array's device address
+ *     (cudaGetSymbolAddress, with that device current) and remembers it; make that first call
+ *     before any stream capture starts.
+ *   - All calls on a device share the one array and it keeps whatever the last call left in it;
+ *     nothing in it needs clearing, because each call writes every partial sum before reading
+ *     it.  Two calls whose kernels overlap on the GPU (different streams) race on it: serialise
+ *     them, or give one of them its own scratch through matgptq_b200_matmul_ws.
+ */
+#define MATGPTQ_B200_STATIC_SCRATCH_BYTES (8 * 1024 * 1024)
+int matgptq_b200_matmul_static_scratch(int64_t bitwidth, int64_t group_size, int64_t n_out, int64_t n_in,
+                                       int64_t batch, const void *w, const void *s, const void *x, void *y,
+                                       void *stream, uint32_t flags);
 
 /*
  * MSB slicing of 8-bit master codes to b bits with round-to-nearest and saturation.

@@ -36,6 +36,8 @@ const char *matgptq_b200_strerror(int status) {
     case MG_ERR_CUDA: return "CUDA runtime call or kernel launch failed";
     case MG_ERR_UNSUPPORTED: return "unsupported shape: K must be a multiple of 128";
     case MG_ERR_ALIGNMENT: return "pointer is not 16-byte aligned";
+    case MATGPTQ_B200_ERR_SCRATCH_TOO_SMALL:
+      return "this shape needs more split-K scratch than the built-in array holds: pass scratch through matgptq_b200_matmul_ws";
     default: return "unknown status";
   }
 }
