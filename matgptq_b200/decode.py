@@ -1,0 +1,264 @@
+"""Whole-model decode over the packed linear layers: a thin Llama-architecture harness.
+
+Stands in for the two serving loops of the reference — vLLM with ``tensor_parallel_size``
+(``inference_lib/inference_demo_vllm.py:16-30``; the all-reduce after row-parallel layers is vLLM's
+``RowParallelLinear``) and the HF-transformers static-cache loop
+(``inference_lib/inference_demo_transformers.py:141-173``) — so that tensor parallelism, per-layer
+bitwidths and CUDA-graph replay are under this package's control.  Every block linear goes through
+``libmatgptq_b200`` (GEMV family for decode, tensor-core path for prefill); attention, RMSNorm, RoPE,
+embedding and the unquantised ``lm_head`` are plain torch ops (plumbing, as in the reference, which
+leaves them to vLLM / transformers).  Weights are random-init (no checkpoints exist here): master codes
+and scales are drawn per layer on the GPU from a seed (``matgptq_b200.synth``).
+
+Tensor parallelism: q/k/v and gate/up are column-parallel (out-features split), o and down are
+row-parallel (in-features split, one all-reduce each), ``lm_head`` is vocabulary-parallel with an
+all-gather of the logits.  One process per GPU over ``torch.distributed`` (NCCL).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import torch
+import torch.distributed as dist
+import torch.nn.functional as F
+
+from . import _native, ops, synth
+
+
+@dataclass
+class LlamaShape:
+    hidden: int
+    intermediate: int
+    n_heads: int
+    n_kv_heads: int
+    n_layers: int
+    vocab: int
+    rope_theta: float = 500000.0
+    eps: float = 1e-5
+
+    @property
+    def head_dim(self) -> int:
+        return self.hidden // self.n_heads
+
+
+LLAMA31_8B = LlamaShape(4096, 14336, 32, 8, 32, 128256)
+LLAMA31_70B = LlamaShape(8192, 28672, 64, 8, 80, 128256)
+
+
+def layer_names(shape: LlamaShape) -> dict[str, int]:
+    """``checkpoint layer name -> parameter count`` of every quantised linear."""
+    d = shape.head_dim
+    out = {}
+    for i in range(shape.n_layers):
+        p = f"model.layers.{i}"
+        out[f"{p}.self_attn.q_proj"] = shape.hidden * shape.hidden
+        out[f"{p}.self_attn.k_proj"] = shape.n_kv_heads * d * shape.hidden
+        out[f"{p}.self_attn.v_proj"] = shape.n_kv_heads * d * shape.hidden
+        out[f"{p}.self_attn.o_proj"] = shape.hidden * shape.hidden
+        out[f"{p}.mlp.gate_proj"] = shape.intermediate * shape.hidden
+        out[f"{p}.mlp.up_proj"] = shape.intermediate * shape.hidden
+        out[f"{p}.mlp.down_proj"] = shape.hidden * shape.intermediate
+    return out
+
+
+class PackedLinear:
+    """One (possibly fused) linear layer: consecutive output segments, each with its own bitwidth."""
+
+    def __init__(self, segments, n_in: int, group_size: int, dtype: torch.dtype, keep_master: bool = False):
+        # segments: list of (rows, bits, qweight_master_u8 [rows, n_in], scales [rows, G])
+        self.n_in = n_in
+        self.group_size = group_size
+        self.flag = _native.FLAG_ASYNC | (_native.FLAG_BF16 if dtype == torch.bfloat16 else 0)
+        self.parts = []
+        self.master = [] if keep_master else None
+        merged = []
+        for rows, bits, q, s in segments:
+            if merged and merged[-1][1] == bits:
+                merged[-1] = (merged[-1][0] + rows, bits, torch.cat([merged[-1][2], q]), torch.cat([merged[-1][3], s]))
+            else:
+                merged.append((rows, bits, q, s))
+        for rows, bits, q, s in merged:
+            packed = torch.ops.matgptq_cuda.slice_pack_matgptq_qweights(q.contiguous(), rows, n_in, 8, bits, group_size, self.flag)
+            scales = torch.ops.matgptq_cuda.reorder_matgptq_scales(s.contiguous(), rows, n_in, group_size)
+            self.parts.append((rows, bits, packed, scales))
+            if keep_master:
+                self.master.append((rows, bits, q.cpu(), s.cpu()))
+        self.n_out = sum(p[0] for p in self.parts)
+
+    def __call__(self, x: torch.Tensor, pdl: bool = False) -> torch.Tensor:
+        flag = self.flag | (_native.FLAG_PDL if pdl else 0)
+        outs = [ops.matmul_matgptq_raw(x, packed, scales, rows, self.n_in, bits, self.group_size, flag)
+                for rows, bits, packed, scales in self.parts]
+        return outs[0] if len(outs) == 1 else torch.cat(outs, dim=-1)
+
+    def weight_bytes(self) -> int:
+        return sum(p.numel() * 4 + s.numel() * 2 for _, _, p, s in self.parts)
+
+
+def _make_segments(names_rows, n_in, n_in_total, col0, bits_of, group_size, dtype, seed_of, dev, row_slices):
+    """Draw master codes/scales of each named layer (full shape from its seed) and cut this rank's shard."""
+    segs = []
+    for (name, rows_total), (r0, r1) in zip(names_rows, row_slices):
+        layer = synth.make_layer(rows_total, n_in_total, group_size, seed=seed_of(name), sym=True, dtype=dtype, device=dev)
+        g0, g1 = col0 // group_size, (col0 + n_in) // group_size
+        q = layer.qweight[r0:r1, col0:col0 + n_in]
+        s = layer.scales[r0:r1, g0:g1]
+        segs.append((r1 - r0, bits_of(name), q, s))
+    return segs
+
+
+class PackedLlama:
+    """Llama-architecture decoder over packed linears, one tensor-parallel rank of it."""
+
+    def __init__(self, shape: LlamaShape, bits, *, group_size: int = 128, dtype: torch.dtype = torch.float16,
+                 tp_rank: int = 0, tp_size: int = 1, seed: int = 0, batch: int = 1, max_seq: int = 256,
+                 device: torch.device | str = "cuda", keep_master: bool = False, pdl: bool = True):
+        self.shape, self.dtype, self.dev = shape, dtype, torch.device(device)
+        self.tp_rank, self.tp_size, self.batch, self.max_seq, self.pdl = tp_rank, tp_size, batch, max_seq, pdl
+        T, r, d = tp_size, tp_rank, shape.head_dim
+        assert shape.n_heads % T == 0 and shape.n_kv_heads % T == 0 and shape.intermediate % (T * 128) == 0
+        assert (shape.hidden // T) % 128 == 0 and shape.vocab % T == 0
+        self.h_loc, self.kv_loc = shape.n_heads // T, shape.n_kv_heads // T
+        names = list(layer_names(shape))
+        bits_of = (lambda n: bits) if isinstance(bits, int) else (lambda n: bits[n])
+        seed_of = lambda n: seed * 100003 + names.index(n)  # noqa: E731
+        H, I = shape.hidden, shape.intermediate
+        qr, kvr, ir = H // T, shape.n_kv_heads * d // T, I // T
+        mk = lambda nr, n_in, n_tot, c0, rs: PackedLinear(  # noqa: E731
+            _make_segments(nr, n_in, n_tot, c0, bits_of, group_size, dtype, seed_of, self.dev, rs), n_in, group_size, dtype, keep_master)
+        self.layers = []
+        gen = torch.Generator(device=self.dev).manual_seed(seed + 17)
+        for i in range(shape.n_layers):
+            p = f"model.layers.{i}"
+            qkv = mk([(f"{p}.self_attn.q_proj", H), (f"{p}.self_attn.k_proj", shape.n_kv_heads * d), (f"{p}.self_attn.v_proj", shape.n_kv_heads * d)],
+                     H, H, 0, [(r * qr, (r + 1) * qr), (r * kvr, (r + 1) * kvr), (r * kvr, (r + 1) * kvr)])
+            o = mk([(f"{p}.self_attn.o_proj", H)], H // T, H, r * (H // T), [(0, H)])
+            gate_up = mk([(f"{p}.mlp.gate_proj", I), (f"{p}.mlp.up_proj", I)], H, H, 0, [(r * ir, (r + 1) * ir)] * 2)
+            down = mk([(f"{p}.mlp.down_proj", H)], I // T, I, r * ir, [(0, H)])
+            norms = [(1.0 + 0.1 * torch.randn(H, generator=gen, device=self.dev)).to(dtype) for _ in range(2)]
+            self.layers.append({"qkv": qkv, "o": o, "gate_up": gate_up, "down": down, "ln1": norms[0], "ln2": norms[1]})
+        self.final_norm = (1.0 + 0.1 * torch.randn(H, generator=gen, device=self.dev)).to(dtype)
+        self.embed = (torch.randn(shape.vocab, H, generator=gen, device=self.dev) * 0.02).to(dtype)
+        v_loc = shape.vocab // T
+        head = (torch.randn(shape.vocab, H, generator=gen, device=self.dev) * 0.02).to(dtype)
+        self.lm_head = head[r * v_loc:(r + 1) * v_loc].contiguous()
+        del head
+        inv = 1.0 / (shape.rope_theta ** (torch.arange(0, d, 2, device=self.dev, dtype=torch.float32) / d))
+        ang = torch.arange(max_seq, device=self.dev, dtype=torch.float32)[:, None] * inv[None, :]
+        self.cos, self.sin = ang.cos(), ang.sin()
+        self.k_cache = [torch.zeros(batch, self.kv_loc, max_seq, d, dtype=dtype, device=self.dev) for _ in range(shape.n_layers)]
+        self.v_cache = [torch.zeros_like(k) for k in self.k_cache]
+        self.key_index = torch.arange(max_seq, device=self.dev)
+
+    # -- pieces ------------------------------------------------------------------------------
+    def linear(self, layer: int, which: str, x: torch.Tensor) -> torch.Tensor:
+        """x [M, n_in] -> [M, n_out] through the packed layer (tests swap this for a dense reference)."""
+        return self.layers[layer][which](x, self.pdl)
+
+    def _rms(self, x, w):
+        xf = x.float()
+        return (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + self.shape.eps)).to(self.dtype) * w
+
+    def _rope(self, t, positions):  # t [B, S, h, d]
+        cos, sin = self.cos[positions][None, :, None, :], self.sin[positions][None, :, None, :]
+        t1, t2 = t.float()[..., 0::2], t.float()[..., 1::2]
+        return torch.stack((t1 * cos - t2 * sin, t1 * sin + t2 * cos), dim=-1).flatten(-2).to(self.dtype)
+
+    def _all_reduce(self, t):
+        if self.tp_size > 1:
+            dist.all_reduce(t)
+        return t
+
+    def forward(self, tokens: torch.Tensor, positions: torch.Tensor) -> torch.Tensor:
+        """tokens [B, S] int64, positions [S] int64 (device) -> logits of the last position [B, vocab] (fp32)."""
+        B, S = tokens.shape
+        d = self.shape.head_dim
+        x = self.embed[tokens].reshape(B * S, -1)
+        mask = (self.key_index[None, :] <= positions[:, None])[None, None]  # [1, 1, S, max_seq]
+        for li, L in enumerate(self.layers):
+            h = self._rms(x, L["ln1"])
+            qkv = self.linear(li, "qkv", h).view(B, S, self.h_loc + 2 * self.kv_loc, d)
+            q = self._rope(qkv[:, :, :self.h_loc], positions)
+            k = self._rope(qkv[:, :, self.h_loc:self.h_loc + self.kv_loc], positions)
+            v = qkv[:, :, self.h_loc + self.kv_loc:]
+            self.k_cache[li].index_copy_(2, positions, k.transpose(1, 2))
+            self.v_cache[li].index_copy_(2, positions, v.transpose(1, 2))
+            att = F.scaled_dot_product_attention(q.transpose(1, 2), self.k_cache[li], self.v_cache[li], attn_mask=mask,
+                                                 enable_gqa=True)
+            att = att.transpose(1, 2).reshape(B * S, self.h_loc * d)
+            x = x + self._all_reduce(self.linear(li, "o", att))
+            h = self._rms(x, L["ln2"])
+            gu = self.linear(li, "gate_up", h)
+            inter = gu.shape[-1] // 2
+            act = F.silu(gu[:, :inter].float()).to(self.dtype) * gu[:, inter:]
+            x = x + self._all_reduce(self.linear(li, "down", act.contiguous()))
+        x = self._rms(x.view(B, S, -1)[:, -1], self.final_norm)
+        logits = F.linear(x, self.lm_head).float()
+        if self.tp_size > 1:
+            parts = [torch.empty_like(logits) for _ in range(self.tp_size)]
+            dist.all_gather(parts, logits)
+            logits = torch.cat(parts, dim=-1)
+        return logits
+
+    def weight_bytes(self) -> int:
+        return sum(L[k].weight_bytes() for L in self.layers for k in ("qkv", "o", "gate_up", "down"))
+
+    # -- generation --------------------------------------------------------------------------
+    @torch.no_grad()
+    def generate(self, prompt: torch.Tensor, new_tokens: int, use_graph: bool = True) -> dict:
+        """Greedy decode. Returns generated tokens [B, new_tokens] and device-timed prefill/decode seconds."""
+        B, P = prompt.shape
+        assert B == self.batch and P + new_tokens <= self.max_seq
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(4)]
+        ev[0].record()
+        logits = self.forward(prompt, torch.arange(P, device=self.dev))
+        ev[1].record()
+        tok = logits.argmax(-1, keepdim=True)
+        out = torch.empty(B, new_tokens, dtype=torch.int64, device=self.dev)
+        out[:, 0:1] = tok
+        pos = torch.full((1,), P, dtype=torch.int64, device=self.dev)
+        step_idx = torch.zeros(1, dtype=torch.int64, device=self.dev)
+
+        def step():
+            nxt = self.forward(tok, pos).argmax(-1, keepdim=True)
+            tok.copy_(nxt)
+            pos.add_(1)
+            step_idx.add_(1)
+            out.index_copy_(1, step_idx, nxt)
+
+        graph = None
+        if use_graph and new_tokens > 2:
+            state = (tok.clone(), pos.clone(), step_idx.clone(), out.clone(), [k.clone() for k in self.k_cache], [v.clone() for v in self.v_cache])
+            s = torch.cuda.Stream(device=self.dev)
+            s.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(s):
+                step()  # warm-up outside capture (loads kernels, NCCL buffers)
+                torch.cuda.synchronize()
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph, stream=s):
+                    step()
+            torch.cuda.current_stream().wait_stream(s)
+            # rewind everything the two trial steps touched
+            tok.copy_(state[0]); pos.copy_(state[1]); step_idx.copy_(state[2]); out.copy_(state[3])
+            for k, k0 in zip(self.k_cache, state[4]):
+                k.copy_(k0)
+            for v, v0 in zip(self.v_cache, state[5]):
+                v.copy_(v0)
+        torch.cuda.synchronize()
+        if self.tp_size > 1:
+            dist.barrier()
+        ev[2].record()
+        for _ in range(new_tokens - 1):
+            if graph is not None:
+                graph.replay()
+            else:
+                step()
+        ev[3].record()
+        torch.cuda.synchronize()
+        return {"tokens": out, "prefill_s": ev[0].elapsed_time(ev[1]) * 1e-3,
+                "decode_s": ev[2].elapsed_time(ev[3]) * 1e-3, "decode_steps": new_tokens - 1}
+
+
+def mixed_bitwidths(shape: LlamaShape, mean_bits: float, seed: int = 0) -> dict[str, int]:
+    """Seeded heterogeneous per-layer assignment from {2,3,4,6,8} with the given parameter-weighted mean."""
+    return synth.bitwidth_assignment(layer_names(shape), mean_bits, seed=seed)
