@@ -311,7 +311,12 @@ def ours_main(args) -> None:
     if rank == 0 and world == 1:
         if not args.no_table:
             extra = per_cell_table(dev, flags)
+            extra["tensor_core_cells"] = run_tensor_core_cells(dev)
         cpu = run_cpu_arm(steps=2, warmup=1)
+    if not args.no_decode:
+        # mixed-precision decode, Llama-3.1-8B architecture, mean 3.0 bits, prompt 128, 128 new tokens
+        dec = [run_decode(world, rank, dev, "8b", batch, 128, 128, 3.0) for batch in ((1, 8, 32) if world == 1 else (1,))]
+        extra["decode"] = dec
 
     if rank != 0:
         if world > 1:
@@ -344,6 +349,87 @@ def ours_main(args) -> None:
     print(json.dumps(line), flush=True)
     if world > 1:
         torch.distributed.destroy_process_group()
+
+
+def run_decode(world: int, rank: int, dev: torch.device, model_name: str, batch: int, prompt_len: int, new_tokens: int,
+               mean_bits: float, layers: int | None = None) -> dict:
+    """Greedy decode of a random-init Llama-architecture model over packed linears: random prompt ids,
+    seeded per-layer bitwidths from {2,3,4,6,8} with the given parameter-weighted mean, one CUDA-graph
+    replay per token; tok/s = generated tokens * batch / device time of the decode phase (max over ranks)."""
+    from matgptq_b200 import decode
+    shape = {"8b": decode.LLAMA31_8B, "70b": decode.LLAMA31_70B}[model_name]
+    if layers:
+        shape = decode.LlamaShape(shape.hidden, shape.intermediate, shape.n_heads, shape.n_kv_heads, layers, shape.vocab)
+    bits = decode.mixed_bitwidths(shape, mean_bits, seed=0)
+    names = decode.layer_names(shape)
+    achieved_bits = sum(bits[n] * names[n] for n in names) / sum(names.values())
+    model = decode.PackedLlama(shape, bits, dtype=torch.float16, tp_rank=rank, tp_size=world, seed=0, batch=batch,
+                               max_seq=prompt_len + new_tokens, device=dev)
+    g = torch.Generator().manual_seed(0)
+    prompt = torch.randint(0, shape.vocab, (batch, prompt_len), generator=g).to(dev)
+    r = model.generate(prompt, new_tokens, use_graph=True)
+    t = torch.tensor([r["decode_s"], r["prefill_s"]], device=dev, dtype=torch.float64)
+    if world > 1:
+        torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
+    decode_s, prefill_s = float(t[0]), float(t[1])
+    wbytes = model.weight_bytes()
+    out = {"model": f"llama-3.1-{model_name} architecture, random init" + (f", {layers} layers" if layers else ""),
+           "tp": world, "batch": batch, "prompt_len": prompt_len, "new_tokens": new_tokens,
+           "mean_bits": round(achieved_bits, 3), "tok_per_s": round(r["decode_steps"] * batch / decode_s, 1),
+           "ms_per_token": round(decode_s / r["decode_steps"] * 1e3, 4), "prefill_ms": round(prefill_s * 1e3, 2),
+           "packed_weight_gb_per_rank": round(wbytes / 1e9, 3),
+           "weight_stream_gbs_per_rank": round(wbytes / (decode_s / r["decode_steps"]) / 1e9, 1)}
+    del model
+    torch.cuda.empty_cache()
+    return out
+
+
+def run_tensor_core_cells(dev: torch.device) -> list:
+    """Tensor-core regime: bf16, M in {32,64,128,256}, b in {3,4,8}, next to torch's dense bf16 GEMM on the
+    dequantised weights.  Cold L2: launches rotate over copies of the weights."""
+    from matgptq_b200 import ops
+    out = []
+    for si, (name, (k, n)) in enumerate(synth.LLAMA3_8B_SHAPES.items()):
+        layer = synth.make_layer(n, k, GROUP, seed=300 + si, sym=True, dtype=torch.bfloat16, device=dev)
+        scales_r = torch.ops.matgptq_cuda.reorder_matgptq_scales(layer.scales, n, k, GROUP)
+        for b in (3, 4, 8):
+            packed = torch.ops.matgptq_cuda.slice_pack_matgptq_qweights(layer.qweight, n, k, 8, b, GROUP, 3)
+            dense = torch.ops.matgptq_cuda.dequantize_matgptq(packed, scales_r, n, k, b, GROUP, 3)
+            copies = max(2, min(16, -(-300 * 1024 * 1024 // (dense.numel() * 2))))
+            packs = [packed] + [packed.clone() for _ in range(copies - 1)]
+            denses = [dense] + [dense.clone() for _ in range(copies - 1)]
+            for m in (32, 64, 128, 256):
+                x = synth.make_activations(m, k, seed=m, dtype=torch.bfloat16, device=dev)
+                y = torch.empty(m, n, dtype=torch.bfloat16, device=dev)
+                need = ops._lib.matgptq_b200_matmul_workspace_bytes(n, k, m)
+                ws = torch.empty(max(need, 16), dtype=torch.uint8, device=dev)
+
+                def ours(i):
+                    ops.matmul_matgptq_raw(x, packs[i % copies], scales_r, n, k, b, GROUP, 3, out=y, workspace=ws if need else None)
+
+                def torch_dense(i):
+                    torch.matmul(x, denses[i % copies].t(), out=y)
+
+                times = {}
+                for label, fn in (("ours", ours), ("dense", torch_dense)):
+                    for i in range(copies):
+                        fn(i)
+                    torch.cuda.synchronize()
+                    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    reps = 2 * copies
+                    e0.record()
+                    for i in range(reps):
+                        fn(i)
+                    e1.record()
+                    torch.cuda.synchronize()
+                    times[label] = e0.elapsed_time(e1) * 1e3 / reps
+                flops = 2.0 * m * n * k
+                out.append({"shape": name, "m": m, "b": b, "us": round(times["ours"], 2), "dense_bf16_us": round(times["dense"], 2),
+                            "tflops": round(flops / times["ours"] / 1e6, 1),
+                            "gbs": round(synth.algorithmic_bytes(n, k, m, b, GROUP) / times["ours"] / 1e3, 1)})
+            del packs, denses
+        del layer
+    return out
 
 
 def run_e2e(cells, dev, flags, steps: int) -> dict:
@@ -399,6 +485,22 @@ def single_cell_main(args) -> None:
                       "algorithmic_bytes": synth.algorithmic_bytes(n, k, m, b, GROUP)}))
 
 
+def decode_main(args) -> None:
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    torch.cuda.set_device(dev)
+    if world > 1:
+        torch.distributed.init_process_group("nccl", device_id=dev)
+    parts = args.decode.split(":")
+    r = run_decode(world, rank, dev, parts[0], int(parts[1]), int(parts[2]), int(parts[3]), float(parts[4]),
+                   int(parts[5]) if len(parts) > 5 else None)
+    if rank == 0:
+        print(json.dumps({"metric": "decode_tokens_per_s", "value": r["tok_per_s"], "unit": "tok/s", "n_gpus": world, **r}), flush=True)
+    if world > 1:
+        torch.distributed.destroy_process_group()
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--cell", type=str, default=None,
@@ -410,8 +512,13 @@ def main() -> None:
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--no-pdl", action="store_true", help="launch without programmatic dependent launch")
     ap.add_argument("--no-table", action="store_true", help="skip the per-cell cold-L2 table")
+    ap.add_argument("--no-decode", action="store_true", help="skip the whole-model decode measurement")
+    ap.add_argument("--decode", type=str, default=None,
+                    help="model:batch:prompt:new:mean_bits[:layers], e.g. 70b:16:512:256:3.5 - only run this decode and exit")
     args = ap.parse_args()
-    if args.cell:
+    if args.decode:
+        decode_main(args)
+    elif args.cell:
         single_cell_main(args)
     elif args.impl == "reference":
         reference_main(args)
