@@ -294,6 +294,9 @@ def ours_main(args) -> None:
             torch.distributed.barrier()
         elapsed_ms = e0.elapsed_time(e1)
         clocks = sampler.stop() if rank == 0 else None
+        # a live CUDA graph that holds NCCL kernels blocks the process group's shutdown
+        graph.reset()
+        del graph
     if world > 1:
         t = torch.tensor([elapsed_ms], device=dev, dtype=torch.float64)
         torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)

@@ -255,6 +255,8 @@ class PackedLlama:
                 step()
         ev[3].record()
         torch.cuda.synchronize()
+        if graph is not None:
+            graph.reset()  # a live graph holding NCCL kernels would block the process group's shutdown
         return {"tokens": out, "prefill_s": ev[0].elapsed_time(ev[1]) * 1e-3,
                 "decode_s": ev[2].elapsed_time(ev[3]) * 1e-3, "decode_steps": new_tokens - 1}
 
