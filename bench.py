@@ -414,18 +414,29 @@ def run_tensor_core_cells(dev: torch.device) -> list:
                     torch.matmul(x, denses[i % copies].t(), out=y)
 
                 times = {}
+                reps = 2 * copies
                 for label, fn in (("ours", ours), ("dense", torch_dense)):
-                    for i in range(copies):
-                        fn(i)
-                    torch.cuda.synchronize()
-                    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                    reps = 2 * copies
-                    e0.record()
-                    for i in range(reps):
-                        fn(i)
-                    e1.record()
-                    torch.cuda.synchronize()
-                    times[label] = e0.elapsed_time(e1) * 1e3 / reps
+                    stream = torch.cuda.Stream(device=dev)
+                    with torch.cuda.stream(stream):
+                        for i in range(copies):
+                            fn(i)
+                        stream.synchronize()
+                        graph = torch.cuda.CUDAGraph()
+                        with torch.cuda.graph(graph, stream=stream):
+                            for i in range(reps):
+                                fn(i)
+                        graph.replay()
+                        stream.synchronize()
+                        ts = []
+                        for _ in range(5):
+                            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                            e0.record(stream)
+                            graph.replay()
+                            e1.record(stream)
+                            stream.synchronize()
+                            ts.append(e0.elapsed_time(e1) * 1e3 / reps)
+                        times[label] = statistics.median(ts)
+                        del graph
                 flops = 2.0 * m * n * k
                 out.append({"shape": name, "m": m, "b": b, "us": round(times["ours"], 2), "dense_bf16_us": round(times["dense"], 2),
                             "tflops": round(flops / times["ours"] / 1e6, 1),

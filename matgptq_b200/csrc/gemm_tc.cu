@@ -9,8 +9,9 @@
 //     block to the exact dense weights of the reference's dequantize()
 //     (round(scale * (code*2^(8-b) - 128)), fp16 or bf16) and store them K-major into a
 //     shared-memory stage in the canonical no-swizzle UMMA layout (8 x 16-byte core
-//     matrices); the same warps copy the activation tile into the 128-byte-swizzled
-//     K-major layout with cp.async;
+//     matrices), with the packed words of the next three blocks already in flight; the
+//     same warps copy the activation tile into the 128-byte-swizzled K-major layout with
+//     cp.async, two pipeline stages ahead of the weights they are decoding;
 //   * a ninth warp issues tcgen05.mma (M = 128 weights rows, N = batch rows, K = 16)
 //     from shared-memory descriptors; D[128, N] lives in tensor memory; completion
 //     of a stage's MMAs releases the stage through tcgen05.commit -> mbarrier;
@@ -34,7 +35,7 @@ namespace mg {
 constexpr int kTcChunkStride = 2080;   // bytes between 16-byte K chunks of the A stage: 128 rows * 16 B + 32 B
                                        // (the 32 bytes spread the four k-chunks a warp stores at once over all banks)
 constexpr int kTcAStageBytes = 8 * kTcChunkStride;  // 8 chunks of 8 in-features
-constexpr int kTcThreads = 9 * 32;
+constexpr int kTcThreads = 9 * 32;  // 8 producer warps and the MMA issuer
 
 struct GemmParams {
   const uint32_t *w;
@@ -142,7 +143,7 @@ __device__ __forceinline__ void tc_load_scales(const uint16_t *s, int tile16, in
 }
 
 template <int B, int GS, bool BF16>
-__global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const GemmParams p) {
+__global__ void __launch_bounds__(kTcThreads, 2) gemm_tc_kernel(const GemmParams p) {
   extern __shared__ unsigned char tc_smem_raw[];
   const uint32_t raw_u32 = smem_u32(tc_smem_raw);
   const uint32_t base_u32 = (raw_u32 + 1023u) & ~1023u;
@@ -171,7 +172,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const GemmParams
   if (warp == 8) {
     if (lane == 0) {
       for (int i = 0; i < stages; ++i) {
-        mbar_init(bar_full + i * 8, 8);
+        mbar_init(bar_full + i * 8, 8);  // the eight producer warps
         mbar_init(bar_empty + i * 8, 1);
       }
       mbar_init(bar_done, 1);
@@ -197,73 +198,91 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const GemmParams
     const bool valid = tile16 < p.N / 16;
     constexpr int BW = BlockTraits<B>::WORDS;
     const uint32_t *wsrc = p.w + (static_cast<size_t>(valid ? tile16 : 0) * p.kblocks + kb_lo) * BW;
-    uint32_t w[2 * B], wn[2 * B];
-    TcScales<GS> sc, scn;
-    if (valid) {
-      load_block<B>(wsrc, lane, wn);
-      tc_load_scales<GS>(p.s, tile16, kb_lo, groups, g, scn);
-    }
-    for (int it = 0; it < nit && !failed; ++it) {
-      const int s = it % stages;
-      if (!mbar_wait(bar_empty + s * 8, ((it / stages) & 1) ^ 1)) {
-        failed = true;
-        report_status(kStatusMmaTimeout);
-        break;
+    // Packed words and scales of three blocks in flight, in statically indexed registers: the block
+    // loop is unrolled by three so that no register is copied while its load is still outstanding.
+    constexpr int kAhead = (B >= 6) ? 2 : 3;
+    uint32_t wq[kAhead][2 * B];
+    TcScales<GS> scq[kAhead];
+#pragma unroll
+    for (int a = 0; a < kAhead; ++a) {
+      if (valid && a < nblk) {
+        load_block<B>(wsrc + static_cast<size_t>(a) * BW, lane, wq[a]);
+        tc_load_scales<GS>(p.s, tile16, kb_lo + a, groups, g, scq[a]);
       }
-      const uint32_t stage_b = base_u32 + plan.off_stages + s * plan.stage_bytes;
-      const uint32_t stage_a = stage_b + plan.b_stage_bytes;
-      const int h = it & 1, kbl = it >> 1;
-      // activation tile: row r, 16-byte chunk c of the 64 in-features, 128-byte swizzle
-      {
-        const uint16_t *xsrc = p.x + static_cast<size_t>(m0) * p.K + static_cast<size_t>(kb_lo + kbl) * 128 + h * 64;
+    }
+    // Activation tile of iteration j: rows m0.., 64 in-features; row r, 16-byte chunk c goes to
+    // r*128 + ((c ^ (r & 7)) << 4) (128-byte swizzle).  It is requested kXAhead iterations early,
+    // one cp.async group per iteration, after the stage it lands in has been released.
+    constexpr int kXAhead = 2;
+    auto request_x = [&](int j) -> bool {
+      if (j < nit) {
+        const int sj = j % stages;
+        if (!mbar_wait(bar_empty + sj * 8, ((j / stages) & 1) ^ 1)) return false;
+        const uint32_t stage_b = base_u32 + plan.off_stages + sj * plan.stage_bytes;
+        const uint16_t *xsrc = p.x + static_cast<size_t>(m0) * p.K + static_cast<size_t>(kb_lo + (j >> 1)) * 128 + (j & 1) * 64;
         for (int idx = tid; idx < mrows * 8; idx += 256) {
           const int r = idx >> 3, c = idx & 7;
           cp_async16(stage_b + r * 128 + ((c ^ (r & 7)) << 4), xsrc + static_cast<size_t>(r) * p.K + c * 8);
         }
       }
-      if (h == 0) {
-#pragma unroll
-        for (int j = 0; j < 2 * B; ++j) w[j] = wn[j];
-        sc = scn;
-        if (valid && kbl + 1 < nblk) {
-          load_block<B>(wsrc + static_cast<size_t>(kbl + 1) * BW, lane, wn);
-          tc_load_scales<GS>(p.s, tile16, kb_lo + kbl + 1, groups, g, scn);
-        }
+      asm volatile("cp.async.commit_group;" ::: "memory");
+      return true;
+    };
+    for (int j = 0; j < kXAhead; ++j) {
+      if (!request_x(j)) {
+        failed = true;
+        report_status(kStatusMmaTimeout);
       }
-      if (valid) {
-        // dense weights of this lane: rows g and g+8, two 16-byte chunks per row
-        auto emit = [&](int jj) {
-          const int gi = (GS == 32) ? jj : 0;
-          uint4 lo, hi;
-          lo.x = dequant_pair<B, BF16>(decode_pair<B>(w, 8 * jj + 0), sc.lo[gi], false, 0);
-          lo.y = dequant_pair<B, BF16>(decode_pair<B>(w, 8 * jj + 2), sc.lo[gi], false, 0);
-          lo.z = dequant_pair<B, BF16>(decode_pair<B>(w, 8 * jj + 4), sc.lo[gi], false, 0);
-          lo.w = dequant_pair<B, BF16>(decode_pair<B>(w, 8 * jj + 6), sc.lo[gi], false, 0);
-          hi.x = dequant_pair<B, BF16>(decode_pair<B>(w, 8 * jj + 1), sc.hi[gi], false, 0);
-          hi.y = dequant_pair<B, BF16>(decode_pair<B>(w, 8 * jj + 3), sc.hi[gi], false, 0);
-          hi.z = dequant_pair<B, BF16>(decode_pair<B>(w, 8 * jj + 5), sc.hi[gi], false, 0);
-          hi.w = dequant_pair<B, BF16>(decode_pair<B>(w, 8 * jj + 7), sc.hi[gi], false, 0);
-          const int chunk = 4 * (jj & 1) + t;
-          unsigned char *dst = base + plan.off_stages + s * plan.stage_bytes + plan.b_stage_bytes +
-                               chunk * kTcChunkStride + (2 * warp) * 128 + g * 16;
-          *reinterpret_cast<uint4 *>(dst) = lo;
-          *reinterpret_cast<uint4 *>(dst + 128) = hi;
-        };
-        if (h == 0) {
-          emit(0);
-          emit(1);
-        } else {
-          emit(2);
-          emit(3);
-        }
-      }
-      asm volatile("cp.async.wait_all;" ::: "memory");
-      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-      __syncwarp();
-      if (lane == 0) mbar_arrive(bar_full + s * 8);
-      (void)stage_a;
     }
-  } else if (lane == 0) {
+    for (int kb0 = 0; kb0 < nblk && !failed; kb0 += kAhead) {
+#pragma unroll
+      for (int a = 0; a < kAhead; ++a) {
+        const int kbl = kb0 + a;
+        if (kbl < nblk && !failed) {
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            const int it = 2 * kbl + h;
+            const int s = it % stages;  // released: request_x(it) waited for it
+            if (!request_x(it + kXAhead)) {
+              failed = true;
+              report_status(kStatusMmaTimeout);
+              break;
+            }
+            if (valid) {
+              // dense weights of this lane: rows g and g+8, two 16-byte chunks per row
+#pragma unroll
+              for (int jj = 2 * h; jj < 2 * h + 2; ++jj) {
+                const int gi = (GS == 32) ? jj : 0;
+                uint4 lo, hi;
+                lo.x = dequant_pair<B, BF16>(decode_pair<B>(wq[a], 8 * jj + 0), scq[a].lo[gi], false, 0);
+                lo.y = dequant_pair<B, BF16>(decode_pair<B>(wq[a], 8 * jj + 2), scq[a].lo[gi], false, 0);
+                lo.z = dequant_pair<B, BF16>(decode_pair<B>(wq[a], 8 * jj + 4), scq[a].lo[gi], false, 0);
+                lo.w = dequant_pair<B, BF16>(decode_pair<B>(wq[a], 8 * jj + 6), scq[a].lo[gi], false, 0);
+                hi.x = dequant_pair<B, BF16>(decode_pair<B>(wq[a], 8 * jj + 1), scq[a].hi[gi], false, 0);
+                hi.y = dequant_pair<B, BF16>(decode_pair<B>(wq[a], 8 * jj + 3), scq[a].hi[gi], false, 0);
+                hi.z = dequant_pair<B, BF16>(decode_pair<B>(wq[a], 8 * jj + 5), scq[a].hi[gi], false, 0);
+                hi.w = dequant_pair<B, BF16>(decode_pair<B>(wq[a], 8 * jj + 7), scq[a].hi[gi], false, 0);
+                const int chunk = 4 * (jj & 1) + t;
+                unsigned char *dst = base + plan.off_stages + s * plan.stage_bytes + plan.b_stage_bytes +
+                                     chunk * kTcChunkStride + (2 * warp) * 128 + g * 16;
+                *reinterpret_cast<uint4 *>(dst) = lo;
+                *reinterpret_cast<uint4 *>(dst + 128) = hi;
+              }
+            }
+            asm volatile("cp.async.wait_group 2;" ::: "memory");  // = kXAhead: the tile of `it` has landed
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_full + s * 8);
+          }
+          // this block's registers are free: fetch the block three ahead
+          if (valid && kbl + kAhead < nblk) {
+            load_block<B>(wsrc + static_cast<size_t>(kbl + kAhead) * BW, lane, wq[a]);
+            tc_load_scales<GS>(p.s, tile16, kb_lo + kbl + kAhead, groups, g, scq[a]);
+          }
+        }
+      }
+    }
+  } else if (warp == 8 && lane == 0) {
     // ------------------------------------------------------------------ MMA issuer
     const uint32_t idesc = umma_instr_desc(BF16 ? 1 : 0, p.ncols);
     for (int it = 0; it < nit && !failed; ++it) {
@@ -343,12 +362,15 @@ __global__ void splitk_reduce_kernel(const float *__restrict__ partial, uint16_t
 // ----------------------------------------------------------------------------
 static int round_up16(int v) { return (v + 15) / 16 * 16; }
 
-// K split of the tensor-core path: enough CTAs to cover the SMs, at least two blocks each.
+// K split of the tensor-core path: the decode is latency bound with eight producer warps per CTA,
+// so aim at two CTAs per SM where the pipeline stages of two CTAs fit in shared memory (up to 128
+// batch rows), one otherwise; at least four blocks of K per CTA.
 int gemm_tc_pick_split(int N, int K, int M, int sm_count) {
   const int ctas = ((N + 127) / 128) * ((M + 255) / 256);
   const int kblocks = K / 128;
+  const int want = (M <= 128) ? 2 * sm_count : sm_count;
   int split = 1;
-  while (split < 8 && ctas * split * 2 <= sm_count + sm_count / 4 && kblocks / (split * 2) >= 2) split *= 2;
+  while (split < 8 && ctas * (split + 1) <= want && kblocks / (split + 1) >= 4) ++split;  // one wave
   return split;
 }
 
@@ -361,8 +383,10 @@ template <int B, int GS, bool BF16>
 static int launch_gemm_tc(GemmParams p, cudaStream_t stream, bool pdl) {
   auto kernel = gemm_tc_kernel<B, GS, BF16>;
   p.ncols = round_up16(p.M < 256 ? p.M : 256);
+  // four stages, or three where that lets a second CTA share the SM
   int stages = 4;
-  while (stages > 2 && tc_plan(p.ncols, stages).total > 200 * 1024) --stages;
+  if (tc_plan(p.ncols, 4).total > 110 * 1024 && tc_plan(p.ncols, 3).total <= 110 * 1024) stages = 3;
+  while (stages > 3 && tc_plan(p.ncols, stages).total > 200 * 1024) --stages;
   p.stages = stages;
   const TcPlan plan = tc_plan(p.ncols, stages);
   static bool opted_in[64] = {};
