@@ -62,12 +62,17 @@ int matgptq_b200_matmul_tuned(int64_t bitwidth, int64_t group_size, int64_t n_ou
                               int warps_per_cta, int split_k);
 
 /*
- * The same product with caller-provided scratch memory.  Batches of 32 rows and more run
- * on the tensor cores (tcgen05); for shapes with few 128-row tiles that path splits K over
- * several CTAs and needs matgptq_b200_matmul_workspace_bytes(...) bytes of device scratch
- * (16-byte aligned; contents undefined before and after; one buffer per stream in flight).
- * Without scratch (workspace NULL, or matgptq_b200_matmul) K is not split.
- *   path: 0 = choose by batch size, 1 = GEMV family, 2 = tensor-core path (any batch size)
+ * The same product with caller-provided scratch memory.  Two kernels want it:
+ *   - batches of 1..4 rows run a persistent GEMV that deals the matrix out evenly over all
+ *     SMs; tiles that span CTAs are completed through a few KB of scratch;
+ *   - batches of 32 rows and more run on the tensor cores (tcgen05); for shapes with few
+ *     128-row tiles that path splits K over several CTAs and parks fp32 partial sums there.
+ * matgptq_b200_matmul_workspace_bytes(...) gives the size (16-byte aligned; contents may be
+ * anything before the call and are undefined after it; one buffer per stream in flight).
+ * Without scratch (workspace NULL, or matgptq_b200_matmul) the cluster GEMV runs for small
+ * batches and K is not split on the tensor-core path.
+ *   path: 0 = choose by batch size, 1 = cluster GEMV, 2 = tensor-core path (any batch size),
+ *         3 = persistent GEMV (status 3 when the shape or the scratch does not allow it)
  *   split_k: 0 = choose; otherwise the number of CTAs along K (tensor-core path: needs
  *            split_k*M*N*4 bytes of scratch)
  * The reference has one kernel pair for all batch sizes and no scratch
@@ -151,7 +156,7 @@ int matgptq_b200_dequantize(const uint32_t *packed, const void *scales, const vo
  * up records a non-zero code instead of hanging, and its output is then undefined.
  * This call synchronises with the device, returns the first code recorded on the
  * current device since the last reset (0 = none; 101 weight copy, 102 activation
- * copy, 103 tensor-core completion) and clears it when reset != 0.  The reference has
+ * copy, 103 tensor-core completion, 104 cross-CTA completion) and clears it when reset != 0.  The reference has
  * no counterpart: its only error path is exit(1) in CHECK_CUDA (csrc/include/common.cuh:44-51).
  */
 int matgptq_b200_device_status(int *status_out, int reset);

@@ -34,7 +34,8 @@ const char *matgptq_b200_strerror(int status) {
     case MG_OK: return "ok";
     case MG_ERR_BAD_ARG: return "bad argument (bitwidth must be 2,3,4,6,8; group size -1,32,128; N % 16 == 0; K % 64 == 0; non-null pointers)";
     case MG_ERR_CUDA: return "CUDA runtime call or kernel launch failed";
-    case MG_ERR_UNSUPPORTED: return "unsupported shape: K must be a multiple of 128";
+    case MG_ERR_UNSUPPORTED:
+      return "unsupported: K must be a multiple of 128, or the forced kernel does not take this shape or scratch size";
     case MG_ERR_ALIGNMENT: return "pointer is not 16-byte aligned";
     case MATGPTQ_B200_ERR_SCRATCH_TOO_SMALL:
       return "this shape needs more split-K scratch than the built-in array holds: pass scratch through matgptq_b200_matmul_ws";
@@ -57,7 +58,7 @@ static int matmul_impl(int64_t bitwidth, int64_t group_size, int64_t n_out, int6
                        int64_t workspace_bytes, int path, int warps_per_cta, int split_k) {
   const int st = check_shape(n_out, n_in, bitwidth, group_size);
   if (st != MG_OK) return st;
-  if (batch < 0 || batch > (1 << 24) || path < 0 || path > 2 || workspace_bytes < 0) return MG_ERR_BAD_ARG;
+  if (batch < 0 || batch > (1 << 24) || path < 0 || path > 3 || workspace_bytes < 0) return MG_ERR_BAD_ARG;
   if (batch == 0) return MG_OK;
   if (!w || !s || !x || !y) return MG_ERR_BAD_ARG;
   if (!aligned16(w) || !aligned16(x) || !aligned16(s) || (reinterpret_cast<uintptr_t>(y) & 1u) ||
@@ -73,8 +74,15 @@ static int matmul_impl(int64_t bitwidth, int64_t group_size, int64_t n_out, int6
                            static_cast<int>(n_in), static_cast<int>(batch), w, s, x, y, workspace, workspace_bytes, bf16,
                            pdl, split_k, cs);
   } else {
-    r = mg::gemv_launch(static_cast<int>(bitwidth), static_cast<int>(group_size), static_cast<int>(n_out),
-                        static_cast<int>(n_in), static_cast<int>(batch), w, s, x, y, bf16, pdl, warps_per_cta, split_k, cs);
+    // smallest batches: the persistent stream-K kernel when the caller gave scratch and the shape fits
+    r = MG_ERR_UNSUPPORTED;
+    if ((path == 0 || path == 3) && warps_per_cta == 0)
+      r = mg::gemv_stream_launch(static_cast<int>(bitwidth), static_cast<int>(group_size), static_cast<int>(n_out),
+                                 static_cast<int>(n_in), static_cast<int>(batch), w, s, x, y, workspace, workspace_bytes,
+                                 bf16, pdl, cs);
+    if (r == MG_ERR_UNSUPPORTED && path != 3)
+      r = mg::gemv_launch(static_cast<int>(bitwidth), static_cast<int>(group_size), static_cast<int>(n_out),
+                          static_cast<int>(n_in), static_cast<int>(batch), w, s, x, y, bf16, pdl, warps_per_cta, split_k, cs);
   }
   if (r != MG_OK) return r;
   if (!(flags & MATGPTQ_B200_FLAG_ASYNC)) {
@@ -104,9 +112,11 @@ int matgptq_b200_matmul_ws(int64_t bitwidth, int64_t group_size, int64_t n_out, 
 }
 
 int64_t matgptq_b200_matmul_workspace_bytes(int64_t n_out, int64_t n_in, int64_t batch) {
-  if (n_out <= 0 || n_in <= 0 || batch < kTensorCoreMinBatch) return 0;
+  if (n_out <= 0 || n_in <= 0 || batch <= 0) return 0;
   int sms = 0;
   if (sm_count_of_current_device(&sms) != MG_OK) sms = 148;
+  if (batch <= 4) return mg::gemv_stream_workspace_bytes(sms);
+  if (batch < kTensorCoreMinBatch) return 0;
   return mg::gemm_tc_workspace_bytes(static_cast<int>(n_out), static_cast<int>(n_in), static_cast<int>(batch), sms);
 }
 
@@ -183,7 +193,10 @@ int matgptq_b200_device_status(int *status_out, int reset) {
   if (r != MG_OK) return r;
   r = mg::gemm_tc_device_status(&b, reset);
   if (r != MG_OK) return r;
-  if (status_out) *status_out = a ? a : b;
+  int c = 0;
+  r = mg::gemv_stream_device_status(&c, reset);
+  if (r != MG_OK) return r;
+  if (status_out) *status_out = a ? a : (b ? b : c);
   return MG_OK;
 }
 

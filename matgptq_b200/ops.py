@@ -256,9 +256,15 @@ def matmul_matgptq_raw(x: torch.Tensor, packed: torch.Tensor, scales: torch.Tens
                                             scales.data_ptr(), x.data_ptr(), out.data_ptr(), stream, flags,
                                             warps_per_cta, split_k)
     else:
-        tensor_core = path == 2 or (path == 0 and batch >= 32)
-        if workspace is None and tensor_core:
-            need = split_k * batch * n_out * 4 if split_k > 1 else _lib.matgptq_b200_matmul_workspace_bytes(n_out, n_in, batch)
+        if workspace is None and path != 1:
+            if path == 2 and split_k > 1:
+                need = split_k * batch * n_out * 4
+            elif path == 2:
+                need = _lib.matgptq_b200_matmul_workspace_bytes(n_out, n_in, max(batch, 32))
+            elif path == 3:
+                need = _lib.matgptq_b200_matmul_workspace_bytes(n_out, n_in, 1)
+            else:
+                need = _lib.matgptq_b200_matmul_workspace_bytes(n_out, n_in, batch)
             if need > 0:
                 workspace = torch.empty(need, dtype=torch.uint8, device=x.device)
         st = _lib.matgptq_b200_matmul_ws(bitwidth, group_size, n_out, n_in, batch, packed.data_ptr(),

@@ -70,8 +70,8 @@ def test_static_scratch_matches_caller_scratch_twice_in_a_row(lib, cuda):
 def test_static_scratch_small_batches_and_limit(lib, cuda):
     n_in, n_out, b = 4096, 4096, 4
     packed, scales_r, flag = _layer(n_out, n_in, b, torch.float16, 3, cuda)
-    # GEMV-sized batch: no scratch involved at all, same answer as the plain entry point
-    x = synth.make_activations(4, n_in, seed=3, dtype=torch.float16, device=cuda)
+    # a batch of the cluster GEMV: no scratch involved at all, same answer
+    x = synth.make_activations(8, n_in, seed=3, dtype=torch.float16, device=cuda)
     y_ws, y_static, need = _both(lib, packed, scales_r, flag, x, n_out, n_in, b)
     assert need == 0 and torch.equal(y_static, y_ws)
     # a shape that wants more than the built-in 8 MiB is refused, and nothing is launched
