@@ -62,17 +62,18 @@ int matgptq_b200_matmul_tuned(int64_t bitwidth, int64_t group_size, int64_t n_ou
                               int warps_per_cta, int split_k);
 
 /*
- * The same product with caller-provided scratch memory.  Two kernels want it:
- *   - batches of 1..4 rows run a persistent GEMV that deals the matrix out evenly over all
- *     SMs; tiles that span CTAs are completed through a few KB of scratch;
- *   - batches of 32 rows and more run on the tensor cores (tcgen05); for shapes with few
- *     128-row tiles that path splits K over several CTAs and parks fp32 partial sums there.
- * matgptq_b200_matmul_workspace_bytes(...) gives the size (16-byte aligned; contents may be
- * anything before the call and are undefined after it; one buffer per stream in flight).
- * Without scratch (workspace NULL, or matgptq_b200_matmul) the cluster GEMV runs for small
- * batches and K is not split on the tensor-core path.
- *   path: 0 = choose by batch size, 1 = cluster GEMV, 2 = tensor-core path (any batch size),
- *         3 = persistent GEMV (status 3 when the shape or the scratch does not allow it)
+ * The same product with caller-provided scratch memory.  Batches of 32 rows and more run
+ * on the tensor cores (tcgen05); for shapes with few 128-row tiles that path splits K over
+ * several CTAs and parks fp32 partial sums in scratch: matgptq_b200_matmul_workspace_bytes(...)
+ * gives the size (16-byte aligned; contents may be anything before the call and are undefined
+ * after it; one buffer per stream in flight).  Without scratch (workspace NULL, or
+ * matgptq_b200_matmul) K is not split.
+ *   path: 0 = choose by batch size (cluster GEMV below 32 rows, tensor cores from 32),
+ *         1 = cluster GEMV, 2 = tensor-core path (any batch size),
+ *         3 = persistent stream-K GEMV, batches 1..4 only, needs
+ *             matgptq_b200_persistent_gemv_workspace_bytes() of scratch; status 3 when the shape
+ *             or the scratch does not allow it.  Kept for experiments: on B200 it is slower
+ *             than path 1 on the Llama-3-8B shapes.
  *   split_k: 0 = choose; otherwise the number of CTAs along K (tensor-core path: needs
  *            split_k*M*N*4 bytes of scratch)
  * The reference has one kernel pair for all batch sizes and no scratch
@@ -84,6 +85,8 @@ int matgptq_b200_matmul_ws(int64_t bitwidth, int64_t group_size, int64_t n_out, 
 
 /* Scratch bytes matgptq_b200_matmul_ws wants for this shape on the current device (0 = none). */
 int64_t matgptq_b200_matmul_workspace_bytes(int64_t n_out, int64_t n_in, int64_t batch);
+/* Scratch bytes of path 3 on the current device (independent of the shape). */
+int64_t matgptq_b200_persistent_gemv_workspace_bytes(void);
 
 /*
  * matgptq_b200_matmul_ws for callers that cannot allocate: hosts whose memory pool already
@@ -150,6 +153,22 @@ int matgptq_b200_reorder_scales_host(const void *scales, void *reordered, int64_
  */
 int matgptq_b200_dequantize(const uint32_t *packed, const void *scales, const void *zeros, void *w_out, int64_t n_out,
                             int64_t n_in, int bitwidth, int64_t group_size, uint32_t flags, void *stream);
+
+/*
+ * Helpers of the decode harness (matgptq_b200/decode.py); the reference leaves these steps to
+ * vLLM / transformers and has no counterpart.  All tensors are device, contiguous, fp16 or bf16
+ * (FLAG_BF16); arithmetic is fp32.
+ *   add_rmsnorm: x[rows,hidden] += delta (when delta != NULL); h = rmsnorm(x) * weight
+ *   rope_kv:     qkv[B,S,(H+2KV)*d] -> q_out[B,H,S,d] rotated (pairs 2i,2i+1); rotated k and v are
+ *                written into the caches [B,KV,max_seq,d] at positions[s]; cos/sin are [max_seq,d/2] fp32
+ *   silu_mul:    gate_up[rows,2*I] -> out[rows,I] = silu(gate) * up
+ */
+int matgptq_b200_add_rmsnorm(void *x, const void *delta, const void *weight, void *h, int64_t rows, int64_t hidden,
+                             float eps, uint32_t flags, void *stream);
+int matgptq_b200_rope_kv(const void *qkv, const int64_t *positions, const float *cos_table, const float *sin_table,
+                         void *q_out, void *k_cache, void *v_cache, int64_t batch, int64_t seq, int64_t n_heads,
+                         int64_t n_kv_heads, int64_t head_dim, int64_t max_seq, uint32_t flags, void *stream);
+int matgptq_b200_silu_mul(const void *gate_up, void *out, int64_t rows, int64_t intermediate, uint32_t flags, void *stream);
 
 /*
  * Waits inside the kernels (on asynchronous copies) are bounded: a kernel that gives

@@ -74,9 +74,11 @@ static int matmul_impl(int64_t bitwidth, int64_t group_size, int64_t n_out, int6
                            static_cast<int>(n_in), static_cast<int>(batch), w, s, x, y, workspace, workspace_bytes, bf16,
                            pdl, split_k, cs);
   } else {
-    // smallest batches: the persistent stream-K kernel when the caller gave scratch and the shape fits
+    // The persistent stream-K kernel runs only on request (path 3): measured on B200 it is slower than
+    // the cluster kernel on every Llama-3-8B shape (its cross-CTA completion and per-CTA set-up cost
+    // about 3 us per launch), so the automatic choice is the cluster kernel.
     r = MG_ERR_UNSUPPORTED;
-    if ((path == 0 || path == 3) && warps_per_cta == 0)
+    if (path == 3 && warps_per_cta == 0)
       r = mg::gemv_stream_launch(static_cast<int>(bitwidth), static_cast<int>(group_size), static_cast<int>(n_out),
                                  static_cast<int>(n_in), static_cast<int>(batch), w, s, x, y, workspace, workspace_bytes,
                                  bf16, pdl, cs);
@@ -111,11 +113,16 @@ int matgptq_b200_matmul_ws(int64_t bitwidth, int64_t group_size, int64_t n_out, 
                      0, split_k);
 }
 
+int64_t matgptq_b200_persistent_gemv_workspace_bytes(void) {
+  int sms = 0;
+  if (sm_count_of_current_device(&sms) != MG_OK) sms = 148;
+  return mg::gemv_stream_workspace_bytes(sms);
+}
+
 int64_t matgptq_b200_matmul_workspace_bytes(int64_t n_out, int64_t n_in, int64_t batch) {
   if (n_out <= 0 || n_in <= 0 || batch <= 0) return 0;
   int sms = 0;
   if (sm_count_of_current_device(&sms) != MG_OK) sms = 148;
-  if (batch <= 4) return mg::gemv_stream_workspace_bytes(sms);
   if (batch < kTensorCoreMinBatch) return 0;
   return mg::gemm_tc_workspace_bytes(static_cast<int>(n_out), static_cast<int>(n_in), static_cast<int>(batch), sms);
 }

@@ -69,6 +69,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
         : "r"(bar), "r"(parity)
         : "memory");
     if (ok) return true;
+    if (it > 4) __nanosleep(40);  // waiting warps should not take issue slots from working ones
   }
   return false;
 }

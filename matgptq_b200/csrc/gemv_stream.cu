@@ -48,9 +48,9 @@ struct StreamParams {
 };
 
 template <int B> struct StreamCfg {
-  static constexpr int CB = (B == 2) ? 2 : 1;        // blocks per ring stage
-  static constexpr int NS = (B <= 4) ? 4 : 3;        // ring stages per warp
-  static constexpr int WARPS = (B == 8) ? 24 : 32;   // warps per CTA
+  static constexpr int CB = (B == 2) ? 4 : (B <= 4) ? 2 : 1;  // blocks per ring stage (1.5 to 2 KB)
+  static constexpr int NS = 3;                               // ring stages per warp
+  static constexpr int WARPS = 24;                           // warps per CTA
 };
 
 struct StreamPlan {
@@ -85,7 +85,7 @@ __device__ __forceinline__ void st_release_u64(unsigned long long *p, unsigned l
 }
 
 template <int B, int GS, bool BF16>
-__global__ void __launch_bounds__(1024, 1) gemv_stream_kernel(const StreamParams p) {
+__global__ void __launch_bounds__(768, 1) gemv_stream_kernel(const StreamParams p) {
   extern __shared__ __align__(128) unsigned char smem_raw[];
   constexpr int CB = StreamCfg<B>::CB, NS = StreamCfg<B>::NS;
   constexpr int WBYTES = BlockTraits<B>::WORDS * 4;
@@ -230,7 +230,9 @@ __global__ void __launch_bounds__(1024, 1) gemv_stream_kernel(const StreamParams
     }
     const unsigned char *stage = ring + st * plan.stage_bytes;
     const int nb = min(CB, cnt - c * CB);
-    for (int cb = 0; cb < nb; ++cb) {
+#pragma unroll
+    for (int cb = 0; cb < CB; ++cb) {
+      if (cb >= nb) break;
       uint32_t w[2 * B];
       {
         const uint32_t *blk = reinterpret_cast<const uint32_t *>(stage + cb * WBYTES);

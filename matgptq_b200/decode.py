@@ -87,6 +87,12 @@ class PackedLinear:
 
     def __call__(self, x: torch.Tensor, pdl: bool = False) -> torch.Tensor:
         flag = self.flag | (_native.FLAG_PDL if pdl else 0)
+        if x.shape[0] == 1 and len(self.parts) > 1:  # one row: every segment writes its slice of the result in place
+            out, col = torch.empty(1, self.n_out, dtype=x.dtype, device=x.device), 0
+            for rows, bits, packed, scales in self.parts:
+                ops.matmul_matgptq_raw(x, packed, scales, rows, self.n_in, bits, self.group_size, flag, out=out[:, col:col + rows])
+                col += rows
+            return out
         outs = [ops.matmul_matgptq_raw(x, packed, scales, rows, self.n_in, bits, self.group_size, flag)
                 for rows, bits, packed, scales in self.parts]
         return outs[0] if len(outs) == 1 else torch.cat(outs, dim=-1)
@@ -155,15 +161,6 @@ class PackedLlama:
         """x [M, n_in] -> [M, n_out] through the packed layer (tests swap this for a dense reference)."""
         return self.layers[layer][which](x, self.pdl)
 
-    def _rms(self, x, w):
-        xf = x.float()
-        return (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + self.shape.eps)).to(self.dtype) * w
-
-    def _rope(self, t, positions):  # t [B, S, h, d]
-        cos, sin = self.cos[positions][None, :, None, :], self.sin[positions][None, :, None, :]
-        t1, t2 = t.float()[..., 0::2], t.float()[..., 1::2]
-        return torch.stack((t1 * cos - t2 * sin, t1 * sin + t2 * cos), dim=-1).flatten(-2).to(self.dtype)
-
     def _all_reduce(self, t):
         if self.tp_size > 1:
             dist.all_reduce(t)
@@ -172,28 +169,40 @@ class PackedLlama:
     def forward(self, tokens: torch.Tensor, positions: torch.Tensor) -> torch.Tensor:
         """tokens [B, S] int64, positions [S] int64 (device) -> logits of the last position [B, vocab] (fp32)."""
         B, S = tokens.shape
-        d = self.shape.head_dim
-        x = self.embed[tokens].reshape(B * S, -1)
-        mask = (self.key_index[None, :] <= positions[:, None])[None, None]  # [1, 1, S, max_seq]
+        d, H = self.shape.head_dim, self.shape.hidden
+        lib = _native.load()
+        flag = _native.FLAG_BF16 if self.dtype == torch.bfloat16 else 0
+        stream = torch.cuda.current_stream(self.dev).cuda_stream
+        rows = B * S
+
+        def add_norm(x, delta, w, h):
+            _native.check(lib.matgptq_b200_add_rmsnorm(x.data_ptr(), delta.data_ptr() if delta is not None else None,
+                                                       w.data_ptr(), h.data_ptr(), rows, H, self.shape.eps, flag, stream),
+                          "add_rmsnorm")
+
+        x = self.embed[tokens].reshape(rows, H)
+        h = torch.empty_like(x)
+        q = torch.empty(B, self.h_loc, S, d, dtype=self.dtype, device=self.dev)
+        act = torch.empty(rows, self.layers[0]["down"].n_in, dtype=self.dtype, device=self.dev)
+        visible = self.key_index[None, :] <= positions[:, None]
+        mask = torch.zeros(S, self.max_seq, dtype=self.dtype, device=self.dev).masked_fill_(~visible, float("-inf"))[None, None]
+        add_norm(x, None, self.layers[0]["ln1"], h)
         for li, L in enumerate(self.layers):
-            h = self._rms(x, L["ln1"])
-            qkv = self.linear(li, "qkv", h).view(B, S, self.h_loc + 2 * self.kv_loc, d)
-            q = self._rope(qkv[:, :, :self.h_loc], positions)
-            k = self._rope(qkv[:, :, self.h_loc:self.h_loc + self.kv_loc], positions)
-            v = qkv[:, :, self.h_loc + self.kv_loc:]
-            self.k_cache[li].index_copy_(2, positions, k.transpose(1, 2))
-            self.v_cache[li].index_copy_(2, positions, v.transpose(1, 2))
-            att = F.scaled_dot_product_attention(q.transpose(1, 2), self.k_cache[li], self.v_cache[li], attn_mask=mask,
-                                                 enable_gqa=True)
-            att = att.transpose(1, 2).reshape(B * S, self.h_loc * d)
-            x = x + self._all_reduce(self.linear(li, "o", att))
-            h = self._rms(x, L["ln2"])
+            qkv = self.linear(li, "qkv", h)
+            _native.check(lib.matgptq_b200_rope_kv(qkv.data_ptr(), positions.data_ptr(), self.cos.data_ptr(), self.sin.data_ptr(),
+                                                   q.data_ptr(), self.k_cache[li].data_ptr(), self.v_cache[li].data_ptr(),
+                                                   B, S, self.h_loc, self.kv_loc, d, self.max_seq, flag, stream), "rope_kv")
+            att = F.scaled_dot_product_attention(q, self.k_cache[li], self.v_cache[li], attn_mask=mask, enable_gqa=True)
+            att = att.transpose(1, 2).reshape(rows, self.h_loc * d)
+            o = self._all_reduce(self.linear(li, "o", att))
+            add_norm(x, o, L["ln2"], h)
             gu = self.linear(li, "gate_up", h)
-            inter = gu.shape[-1] // 2
-            act = F.silu(gu[:, :inter].float()).to(self.dtype) * gu[:, inter:]
-            x = x + self._all_reduce(self.linear(li, "down", act.contiguous()))
-        x = self._rms(x.view(B, S, -1)[:, -1], self.final_norm)
-        logits = F.linear(x, self.lm_head).float()
+            _native.check(lib.matgptq_b200_silu_mul(gu.data_ptr(), act.data_ptr(), rows, act.shape[1], flag, stream), "silu_mul")
+            dn = self._all_reduce(self.linear(li, "down", act))
+            nxt = self.layers[li + 1]["ln1"] if li + 1 < len(self.layers) else self.final_norm
+            add_norm(x, dn, nxt, h)
+        last = h.view(B, S, H)[:, -1]
+        logits = F.linear(last, self.lm_head).float()
         if self.tp_size > 1:
             parts = [torch.empty_like(logits) for _ in range(self.tp_size)]
             dist.all_gather(parts, logits)

@@ -262,7 +262,7 @@ def matmul_matgptq_raw(x: torch.Tensor, packed: torch.Tensor, scales: torch.Tens
             elif path == 2:
                 need = _lib.matgptq_b200_matmul_workspace_bytes(n_out, n_in, max(batch, 32))
             elif path == 3:
-                need = _lib.matgptq_b200_matmul_workspace_bytes(n_out, n_in, 1)
+                need = _lib.matgptq_b200_persistent_gemv_workspace_bytes()
             else:
                 need = _lib.matgptq_b200_matmul_workspace_bytes(n_out, n_in, batch)
             if need > 0:

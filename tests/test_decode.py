@@ -105,3 +105,64 @@ def test_tensor_parallel_sharding_two_cpu_ranks():
         p.join(120)
         assert p.exitcode == 0
     assert out.get(timeout=5) is True
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_decode_helper_kernels_match_torch(cuda, dtype):
+    """add_rmsnorm, rope_kv and silu_mul against the same arithmetic in torch (fp32 inside, results rounded
+    to the model dtype at the same places)."""
+    from matgptq_b200 import _native
+    lib = _native.load()
+    flag = _native.FLAG_BF16 if dtype == torch.bfloat16 else 0
+    stream = torch.cuda.current_stream(cuda).cuda_stream
+    g = torch.Generator(device=cuda).manual_seed(5)
+    rows, hidden, eps = 7, 384, 1e-5
+    x = torch.randn(rows, hidden, generator=g, device=cuda).to(dtype)
+    delta = torch.randn(rows, hidden, generator=g, device=cuda).to(dtype)
+    w = (1 + 0.1 * torch.randn(hidden, generator=g, device=cuda)).to(dtype)
+    for use_delta in (False, True):
+        xs, h = x.clone(), torch.empty_like(x)
+        _native.check(lib.matgptq_b200_add_rmsnorm(xs.data_ptr(), delta.data_ptr() if use_delta else None, w.data_ptr(),
+                                                   h.data_ptr(), rows, hidden, eps, flag, stream), "add_rmsnorm")
+        x_ref = (x + delta) if use_delta else x
+        xf = x_ref.float()
+        h_ref = (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps)).to(dtype) * w
+        assert torch.equal(xs, x_ref)
+        assert (h.float() - h_ref.float()).abs().max() <= 2 * torch.finfo(dtype).eps * h_ref.float().abs().max()
+
+    B, S, H, KV, d, max_seq = 2, 5, 4, 2, 64, 16
+    qkv = torch.randn(B, S, (H + 2 * KV) * d, generator=g, device=cuda).to(dtype)
+    positions = torch.tensor([3, 4, 5, 6, 7], device=cuda)
+    inv = 1.0 / (10000.0 ** (torch.arange(0, d, 2, device=cuda, dtype=torch.float32) / d))
+    ang = torch.arange(max_seq, device=cuda, dtype=torch.float32)[:, None] * inv[None, :]
+    cos, sin = ang.cos().contiguous(), ang.sin().contiguous()
+    q = torch.empty(B, H, S, d, dtype=dtype, device=cuda)
+    kc = torch.zeros(B, KV, max_seq, d, dtype=dtype, device=cuda)
+    vc = torch.zeros_like(kc)
+    _native.check(lib.matgptq_b200_rope_kv(qkv.data_ptr(), positions.data_ptr(), cos.data_ptr(), sin.data_ptr(), q.data_ptr(),
+                                           kc.data_ptr(), vc.data_ptr(), B, S, H, KV, d, max_seq, flag, stream), "rope_kv")
+
+    def rope(t):  # [B, S, h, d]
+        tf = t.float()
+        a, c = tf[..., 0::2], tf[..., 1::2]
+        cs, sn = cos[positions][None, :, None, :], sin[positions][None, :, None, :]
+        return torch.stack([a * cs - c * sn, a * sn + c * cs], dim=-1).flatten(-2).to(dtype)
+
+    parts = qkv.view(B, S, H + 2 * KV, d)
+    q_ref = rope(parts[:, :, :H]).transpose(1, 2)
+    k_ref = rope(parts[:, :, H:H + KV]).transpose(1, 2)
+    v_ref = parts[:, :, H + KV:].transpose(1, 2)
+    tol = 2 * torch.finfo(dtype).eps * 4
+    assert (q.float() - q_ref.float()).abs().max() <= tol * q_ref.float().abs().max()
+    assert (kc[:, :, 3:8].float() - k_ref.float()).abs().max() <= tol * k_ref.float().abs().max()
+    assert torch.equal(vc[:, :, 3:8], v_ref)
+    assert kc[:, :, :3].abs().max() == 0 and kc[:, :, 8:].abs().max() == 0 and vc[:, :, 8:].abs().max() == 0
+
+    inter = 320
+    gu = torch.randn(rows, 2 * inter, generator=g, device=cuda).to(dtype)
+    out = torch.empty(rows, inter, dtype=dtype, device=cuda)
+    _native.check(lib.matgptq_b200_silu_mul(gu.data_ptr(), out.data_ptr(), rows, inter, flag, stream), "silu_mul")
+    ref = F.silu(gu[:, :inter].float()).to(dtype) * gu[:, inter:]
+    assert (out.float() - ref.float()).abs().max() <= 4 * torch.finfo(dtype).eps * ref.float().abs().max()
+    assert lib.matgptq_b200_add_rmsnorm(None, None, w.data_ptr(), h.data_ptr(), 1, hidden, eps, flag, stream) != 0

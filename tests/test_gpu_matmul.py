@@ -169,7 +169,7 @@ def test_persistent_gemv_llama_shapes(cuda, b, shape, m):
     from matgptq_b200 import _native, ops
     n_in, n_out = shape
     packed, scales_r, _, flag = _layer_and_ref(n_out, n_in, 128, b, torch.float16, 5, cuda)
-    need = _native.load().matgptq_b200_matmul_workspace_bytes(n_out, n_in, m)
+    need = _native.load().matgptq_b200_persistent_gemv_workspace_bytes()
     assert need > 0
     ws = torch.randint(0, 255, (need,), dtype=torch.uint8, device=cuda)  # arbitrary contents are allowed
     xs = [synth.make_activations(m, n_in, seed=s, dtype=torch.float16, device=cuda) for s in range(3)]
