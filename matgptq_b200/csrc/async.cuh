@@ -55,23 +55,34 @@ __device__ __forceinline__ void bulk_copy_g2s(uint32_t dst, const void *src, uin
 
 constexpr uint32_t kWaitPolls = 1u << 22;
 
-// Returns false when the phase did not complete within kWaitPolls polls.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n"
+      "  .reg .pred p;\n"
+      "  mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+      "  selp.u32 %0, 1, 0, p;\n"
+      "}\n"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+
+// The rare path of mbar_wait, kept out of line so that the loops that wait stay small.
+static __device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity) {
   for (uint32_t it = 0; it < kWaitPolls; ++it) {
-    uint32_t ok;
-    asm volatile(
-        "{\n"
-        "  .reg .pred p;\n"
-        "  mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
-        "  selp.u32 %0, 1, 0, p;\n"
-        "}\n"
-        : "=r"(ok)
-        : "r"(bar), "r"(parity)
-        : "memory");
-    if (ok) return true;
+    if (mbar_try_wait(bar, parity)) return true;
     if (it > 4) __nanosleep(40);  // waiting warps should not take issue slots from working ones
   }
   return false;
+}
+
+// Returns false when the phase did not complete within kWaitPolls polls.  try_wait itself blocks for a
+// hardware-defined time, so the first poll succeeds whenever the data is not far away.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+  if (mbar_try_wait(bar, parity)) return true;
+  return mbar_wait_slow(bar, parity);
 }
 
 __device__ __forceinline__ void report_status(int code) { atomicCAS(&g_device_status, 0, code); }

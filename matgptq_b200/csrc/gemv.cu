@@ -17,9 +17,10 @@
 //   * the R warps of a CTA cover R consecutive row tiles over the same K slice and
 //     share the activation slice staged once in shared memory;
 //   * K is split over the S CTAs of a thread-block cluster (split-K for skinny
-//     shapes); partial sums meet in distributed shared memory and are added in a
-//     fixed order, so results do not depend on scheduling and no global scratch
-//     or atomics are used;
+//     shapes); every CTA stores its partial sums into the shared memory of the CTA
+//     that owns the columns (distributed shared memory), which adds them in a fixed
+//     order after one cluster barrier, so results do not depend on scheduling and no
+//     global scratch or atomics are used;
 //   * the weight copies of the first stages are issued before griddepcontrol.wait,
 //     so with programmatic dependent launch they overlap the previous kernel's tail;
 //   * every mbarrier wait is bounded (async.cuh): on a timeout the kernel records a
@@ -95,18 +96,19 @@ __global__ void __launch_bounds__(256, 2) gemv_kernel(const GemvParams p) {
   extern __shared__ __align__(128) unsigned char smem_raw[];
 
   const int lane = threadIdx.x & 31;
-  const int warp = threadIdx.x >> 5;
+  const int warp = __shfl_sync(0xffffffffu, threadIdx.x >> 5, 0);  // the shuffle tells the compiler it is warp-uniform
   const int R = blockDim.x >> 5;
   const int g = lane >> 2, t = lane & 3;
   const int S = p.split;
   const int crank = (S > 1) ? static_cast<int>(cg::this_cluster().block_rank()) : 0;
-  const int rg = blockIdx.x / S;
+  const int log2s = 31 - __clz(S);  // S is a power of two (checked by the host)
+  const int rg = blockIdx.x >> log2s;
   const int tile = rg * R + warp;
   const bool active = tile < p.tiles;
-  const int kb_lo = static_cast<int>(static_cast<long long>(crank) * p.kblocks / S);
-  const int kb_hi = static_cast<int>(static_cast<long long>(crank + 1) * p.kblocks / S);
+  const int kb_lo = (crank * p.kblocks) >> log2s;
+  const int kb_hi = ((crank + 1) * p.kblocks) >> log2s;
   const int nblk = kb_hi - kb_lo;
-  const int max_nblk = (p.kblocks + S - 1) / S;
+  const int max_nblk = (p.kblocks + S - 1) >> log2s;
   const int m0 = blockIdx.y * (NT * 8);
   const int mvalid = min(p.M - m0, NT * 8);
   const int groups = (GS == -1) ? 1 : p.K / GS;
@@ -121,11 +123,12 @@ __global__ void __launch_bounds__(256, 2) gemv_kernel(const GemvParams p) {
   const uint32_t bar_full0 = smem_base + plan.off_bars + warp * kStages * 8;  // this warp's ring barriers
   const uint32_t bar_x0 = smem_base + plan.off_bars + R * kStages * 8;        // two activation barriers
   float *red = reinterpret_cast<float *>(smem_raw + plan.off_red);
-  const unsigned char *ring = smem_raw + plan.off_ring + warp * kStages * plan.stage_bytes;
+  const unsigned char *ring = smem_raw + plan.off_ring + warp * kStages * plan.stage_bytes;  // this warp's stages
   const uint32_t ring_u32 = smem_base + plan.off_ring + warp * kStages * plan.stage_bytes;
   const int xstride = plan.xstride_h;
   const int rstride = plan.rstride;
-  const int SCB = plan.scale_bytes_per_block;
+  constexpr int SCB = (GS == -1) ? 0 : (GS == 32 ? 128 : 32);  // scale bytes per block
+  constexpr int kStageBytes = CB * (WBYTES + SCB);
 
   if (lane == 0) {
     for (int i = 0; i < kStages; ++i) mbar_init(bar_full0 + i * 8, 1);
@@ -136,6 +139,9 @@ __global__ void __launch_bounds__(256, 2) gemv_kernel(const GemvParams p) {
     mbar_init_fence();
   }
   __syncthreads();
+  // Tell the cluster that this CTA is running; the matching wait stands before the first store into a
+  // peer's shared memory, long after every peer has arrived.
+  if (S > 1) asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
 
   const int nchunks = (nblk + CB - 1) / CB;
   const unsigned char *wsrc = reinterpret_cast<const unsigned char *>(p.w) +
@@ -143,19 +149,25 @@ __global__ void __launch_bounds__(256, 2) gemv_kernel(const GemvParams p) {
   const unsigned char *ssrc = reinterpret_cast<const unsigned char *>(p.s) +
                               (static_cast<size_t>(active ? tile : 0) * groups) * 32 + static_cast<size_t>(kb_lo) * SCB;
 
-  // lane 0: fill ring stage (c % kStages) with chunk c (weights, then the scales of its blocks)
-  auto issue_chunk = [&](int c) {
-    const int nb = min(CB, nblk - c * CB);
-    const int st = c % kStages;
-    const uint32_t bar = bar_full0 + st * 8;
-    const uint32_t dst = ring_u32 + st * plan.stage_bytes;
-    mbar_arrive_expect_tx(bar, nb * (WBYTES + SCB));
-    bulk_copy_g2s(dst, wsrc + static_cast<size_t>(c) * CB * WBYTES, nb * WBYTES, bar);
-    if (GS != -1) bulk_copy_g2s(dst + CB * WBYTES, ssrc + static_cast<size_t>(c) * CB * SCB, nb * SCB, bar);
+  // Producer state (used by lane 0): the next chunk to request, as running pointers, so that a refill costs no
+  // multiplications.  issue_next() fills the ring stage at byte offset `off` / barrier `bar` with that chunk.
+  int issue_left = nblk;  // blocks not requested yet
+  auto issue_next = [&](uint32_t off, uint32_t bar) {  // called by every lane; lane 0 issues the copies
+    const int nb = min(CB, issue_left);
+    if (lane == 0) {
+      mbar_arrive_expect_tx(bar, nb * (WBYTES + SCB));
+      bulk_copy_g2s(ring_u32 + off, wsrc, nb * WBYTES, bar);
+      if (GS != -1) bulk_copy_g2s(ring_u32 + off + CB * WBYTES, ssrc, nb * SCB, bar);
+    }
+    wsrc += CB * WBYTES;
+    ssrc += CB * SCB;
+    issue_left -= CB;
   };
 
-  if (active && lane == 0) {
-    for (int c = 0; c < kStages && c < nchunks; ++c) issue_chunk(c);
+  if (active) {
+#pragma unroll
+    for (int c = 0; c < kStages; ++c)
+      if (c < nchunks) issue_next(c * kStageBytes, bar_full0 + c * 8);
   }
 
   // Everything above reads only weights and scales, which no kernel writes.  The
@@ -189,14 +201,30 @@ __global__ void __launch_bounds__(256, 2) gemv_kernel(const GemvParams p) {
   constexpr float kNegZero = -static_cast<float>(BlockTraits<B>::ZERO) * 5.9604644775390625e-08f;  // -Z * 2^-24
   float *sums = reinterpret_cast<float *>(smem_raw + plan.off_sums);
 
+  // Loop-invariant per-lane addresses: everything inside the block loop is base + running offset + constant.
+  const unsigned char *w_lane = ring + lane * 16;                        // 16-byte vectors of the packed words
+  const unsigned char *w_tail = ring + BlockTraits<B>::NV * 512 + lane * 8;  // the 8-byte tail (3-bit blocks)
+  const unsigned char *s_lane = ring + CB * WBYTES + g * 2;              // scales of rows g and g+8
+  const uint16_t *x_lane[NT];
+#pragma unroll
+  for (int nt = 0; nt < NT; ++nt)
+    x_lane[nt] = reinterpret_cast<const uint16_t *>(smem_raw + plan.off_x) + min(nt * 8 + g, mvalid - 1) * xstride + 8 * t;
+  const float *z_lane = sums + 2 * t;
+  const int xbuf_halves = plan.xrows * xstride;
+  constexpr int kSumsPerBlock = ((GS == 32) ? 4 : 1) * NT * 8;
+
+  // Consumer state of the ring: stage byte offset, barrier and parity of the next chunk.
+  uint32_t st_off = 0, st_bar = bar_full0, st_parity = 0;
+  int left = nblk;  // blocks not consumed yet
+
   bool failed = false;
   for (int xi = 0; xi < nxst; ++xi) {
     if (!failed && !mbar_wait(bar_x0 + (xi & 1) * 8, (xi >> 1) & 1)) {
       failed = true;
       report_status(kStatusActivationCopyTimeout);
     }
-    uint16_t *xbuf = reinterpret_cast<uint16_t *>(smem_raw + plan.off_x) + (xi & 1) * plan.xrows * xstride;
-    float *xsum = sums + (xi & 1) * kXBlocks * plan.sums_per_block;
+    uint16_t *xbuf = reinterpret_cast<uint16_t *>(smem_raw + plan.off_x) + (xi & 1) * xbuf_halves;
+    float *xsum = sums + (xi & 1) * kXBlocks * kSumsPerBlock;
     const int st_blocks = min(kXBlocks, nblk - xi * kXBlocks);
 
     // bf16 activations become fp16 in place (saturating at +-65504): the type the tensor
@@ -228,146 +256,162 @@ __global__ void __launch_bounds__(256, 2) gemv_kernel(const GemvParams p) {
       const uint32_t ones[4] = {0x3C003C00u, 0x3C003C00u, 0x3C003C00u, 0x3C003C00u};
 #pragma unroll
       for (int nt = 0; nt < NT; ++nt) {
-        const int xrow = min(nt * 8 + g, mvalid - 1);
+        const uint16_t *xp = x_lane[nt] + (xi & 1) * xbuf_halves + blk * 128;
         float sacc[4];
 #pragma unroll
         for (int jj = 0; jj < 4; ++jj) {
-          const uint4 xv = *reinterpret_cast<const uint4 *>(xbuf + xrow * xstride + blk * 128 + 32 * jj + 8 * t);
+          const uint4 xv = *reinterpret_cast<const uint4 *>(xp + 32 * jj);
           if (GS == 32 || jj == 0)
             mma16816<true>(sacc, ones, xv.x, xv.y);
           else
             mma16816<false>(sacc, ones, xv.x, xv.y);
           mma16816<false>(sacc, ones, xv.z, xv.w);
           if (GS == 32 && g == 0)
-            *reinterpret_cast<float2 *>(xsum + blk * plan.sums_per_block + jj * (NT * 8) + nt * 8 + 2 * t) =
+            *reinterpret_cast<float2 *>(xsum + blk * kSumsPerBlock + jj * (NT * 8) + nt * 8 + 2 * t) =
                 make_float2(kNegZero * sacc[0], kNegZero * sacc[1]);
         }
         if (GS != 32 && g == 0)
-          *reinterpret_cast<float2 *>(xsum + blk * plan.sums_per_block + nt * 8 + 2 * t) =
+          *reinterpret_cast<float2 *>(xsum + blk * kSumsPerBlock + nt * 8 + 2 * t) =
               make_float2(kNegZero * sacc[0], kNegZero * sacc[1]);
       }
     }
     __syncthreads();
 
-    const int c_lo = xi * (kXBlocks / CB);
-    const int c_hi = min(nchunks, c_lo + kXBlocks / CB);
     if (active && !failed) {
-      for (int c = c_lo; c < c_hi; ++c) {
-        const int st = c % kStages;
-        if (!mbar_wait(bar_full0 + st * 8, (c / kStages) & 1)) {
-          failed = true;
-          report_status(kStatusWeightCopyTimeout);
-          break;
-        }
-        const unsigned char *stage = ring + st * plan.stage_bytes;
-        const int nb = min(CB, nblk - c * CB);
-        auto do_block = [&](int cb) {
-            const int bi = c * CB + cb - xi * kXBlocks;  // block inside the x stage
-            uint32_t w[2 * B];
-            {
-              const uint32_t *blk = reinterpret_cast<const uint32_t *>(stage + cb * WBYTES);
+      // running offsets inside this activation stage: halves into the x rows, floats into the sums
+      int x_off = (xi & 1) * xbuf_halves;
+      int z_off = (xi & 1) * kXBlocks * kSumsPerBlock;
+      const int stage_blocks = min(kXBlocks, left);
+      const int full_chunks = stage_blocks / CB, rem_blocks = stage_blocks - full_chunks * CB;
+      auto do_block = [&](int cb) {
+          uint32_t w[2 * B];
+          {
+            const unsigned char *blk = w_lane + st_off + cb * WBYTES;
 #pragma unroll
-              for (int v = 0; v < BlockTraits<B>::NV; ++v) {
-                const uint4 q = *reinterpret_cast<const uint4 *>(blk + v * 128 + lane * 4);
-                w[4 * v + 0] = q.x;
-                w[4 * v + 1] = q.y;
-                w[4 * v + 2] = q.z;
-                w[4 * v + 3] = q.w;
-              }
-              if constexpr (BlockTraits<B>::TAIL == 2) {
-                const uint2 q = *reinterpret_cast<const uint2 *>(blk + BlockTraits<B>::NV * 128 + lane * 2);
-                w[4 * BlockTraits<B>::NV + 0] = q.x;
-                w[4 * BlockTraits<B>::NV + 1] = q.y;
-              }
+            for (int v = 0; v < BlockTraits<B>::NV; ++v) {
+              const uint4 q = *reinterpret_cast<const uint4 *>(blk + v * 512);
+              w[4 * v + 0] = q.x;
+              w[4 * v + 1] = q.y;
+              w[4 * v + 2] = q.z;
+              w[4 * v + 3] = q.w;
             }
-            const uint16_t *sblk = reinterpret_cast<const uint16_t *>(stage + CB * WBYTES + cb * SCB);
-            const float *bsum = xsum + bi * plan.sums_per_block;
-
-            // lanes whose batch column does not exist read the last valid row: their
-            // accumulator columns are never written out
-            uint4 xb[4][NT];
-#pragma unroll
-            for (int nt = 0; nt < NT; ++nt) {
-              const int xrow = min(nt * 8 + g, mvalid - 1);
-#pragma unroll
-              for (int jj = 0; jj < 4; ++jj)
-                xb[jj][nt] = *reinterpret_cast<const uint4 *>(xbuf + xrow * xstride + bi * 128 + 32 * jj + 8 * t);
+            if constexpr (BlockTraits<B>::TAIL == 2) {
+              const uint2 q = *reinterpret_cast<const uint2 *>(w_tail + st_off + cb * WBYTES);
+              w[4 * BlockTraits<B>::NV + 0] = q.x;
+              w[4 * BlockTraits<B>::NV + 1] = q.y;
             }
+          }
+          const uint16_t *sblk = reinterpret_cast<const uint16_t *>(s_lane + st_off + cb * SCB);  // [0]: row g, [8]: row g+8
+          const float *bsum = z_lane + z_off + cb * kSumsPerBlock;
 
-            if constexpr (GS == 32) {
-              // one group per pair of k-steps: each k-step gets its own accumulator
+          // lanes whose batch column does not exist read the last valid row: their
+          // accumulator columns are never written out
+          uint4 xb[4][NT];
 #pragma unroll
-              for (int jj = 0; jj < 4; ++jj) {
-                float d0[NT][4], d1[NT][4];
-                uint32_t a0[4], a1[4];
+          for (int nt = 0; nt < NT; ++nt) {
+            const uint16_t *xp = x_lane[nt] + x_off + cb * 128;
 #pragma unroll
-                for (int q = 0; q < 4; ++q) {
-                  a0[q] = field_pair<B>(w, 8 * jj + q, 0u);
-                  a1[q] = field_pair<B>(w, 8 * jj + 4 + q, 0u);
-                }
-                const float f0 = 1.f / static_cast<float>(1 << kstep_offset<B>(2 * jj));
-                const float f1 = 1.f / static_cast<float>(1 << kstep_offset<B>(2 * jj + 1));
-                const float slo = scale_to_float<BF16>(sblk[jj * 16 + g]);
-                const float shi = scale_to_float<BF16>(sblk[jj * 16 + g + 8]);
+            for (int jj = 0; jj < 4; ++jj) xb[jj][nt] = *reinterpret_cast<const uint4 *>(xp + 32 * jj);
+          }
+
+          if constexpr (GS == 32) {
+            // one group per pair of k-steps: each k-step gets its own accumulator
 #pragma unroll
-                for (int nt = 0; nt < NT; ++nt) {
-                  mma16816<true>(d0[nt], a0, xb[jj][nt].x, xb[jj][nt].y);
-                  mma16816<true>(d1[nt], a1, xb[jj][nt].z, xb[jj][nt].w);
-                  const float2 zs = *reinterpret_cast<const float2 *>(bsum + jj * (NT * 8) + nt * 8 + 2 * t);
-                  yacc[nt][0] = fmaf(slo, fmaf(d1[nt][0], f1, fmaf(d0[nt][0], f0, zs.x)), yacc[nt][0]);
-                  yacc[nt][1] = fmaf(slo, fmaf(d1[nt][1], f1, fmaf(d0[nt][1], f0, zs.y)), yacc[nt][1]);
-                  yacc[nt][2] = fmaf(shi, fmaf(d1[nt][2], f1, fmaf(d0[nt][2], f0, zs.x)), yacc[nt][2]);
-                  yacc[nt][3] = fmaf(shi, fmaf(d1[nt][3], f1, fmaf(d0[nt][3], f0, zs.y)), yacc[nt][3]);
-                }
+            for (int jj = 0; jj < 4; ++jj) {
+              float d0[NT][4], d1[NT][4];
+              uint32_t a0[4], a1[4];
+#pragma unroll
+              for (int q = 0; q < 4; ++q) {
+                a0[q] = field_pair<B>(w, 8 * jj + q, 0u);
+                a1[q] = field_pair<B>(w, 8 * jj + 4 + q, 0u);
               }
-            } else {
-              float acc[NCH][NT][4];
-#pragma unroll
-              for (int i = 0; i < 8; ++i) {
-                uint32_t a[4];
-#pragma unroll
-                for (int q = 0; q < 4; ++q) a[q] = field_pair<B>(w, 4 * i + q, 0u);
-                #pragma unroll
-                for (int nt = 0; nt < NT; ++nt) {
-                  const uint32_t b0 = (i & 1) ? xb[i >> 1][nt].z : xb[i >> 1][nt].x;
-                  const uint32_t b1 = (i & 1) ? xb[i >> 1][nt].w : xb[i >> 1][nt].y;
-                  if (Chains<B>::first(i))
-                    mma16816<true>(acc[Chains<B>::of(i)][nt], a, b0, b1);
-                  else
-                    mma16816<false>(acc[Chains<B>::of(i)][nt], a, b0, b1);
-                }
-              }
-              float slo = 1.f, shi = 1.f;
-              if constexpr (GS == 128) {
-                slo = scale_to_float<BF16>(sblk[g]);
-                shi = scale_to_float<BF16>(sblk[g + 8]);
-              }
+              const float f0 = 1.f / static_cast<float>(1 << kstep_offset<B>(2 * jj));
+              const float f1 = 1.f / static_cast<float>(1 << kstep_offset<B>(2 * jj + 1));
+              const float slo = scale_to_float<BF16>(sblk[jj * 16]);
+              const float shi = scale_to_float<BF16>(sblk[jj * 16 + 8]);
 #pragma unroll
               for (int nt = 0; nt < NT; ++nt) {
-                const float2 zs = *reinterpret_cast<const float2 *>(bsum + nt * 8 + 2 * t);
-                float tsum[4] = {zs.x, zs.y, zs.x, zs.y};
-#pragma unroll
-                for (int ch = 0; ch < NCH; ++ch)
-#pragma unroll
-                  for (int e = 0; e < 4; ++e) tsum[e] = fmaf(acc[ch][nt][e], Chains<B>::inv_factor(ch), tsum[e]);
-                yacc[nt][0] = fmaf(slo, tsum[0], yacc[nt][0]);
-                yacc[nt][1] = fmaf(slo, tsum[1], yacc[nt][1]);
-                yacc[nt][2] = fmaf(shi, tsum[2], yacc[nt][2]);
-                yacc[nt][3] = fmaf(shi, tsum[3], yacc[nt][3]);
+                mma16816<true>(d0[nt], a0, xb[jj][nt].x, xb[jj][nt].y);
+                mma16816<true>(d1[nt], a1, xb[jj][nt].z, xb[jj][nt].w);
+                const float2 zs = *reinterpret_cast<const float2 *>(bsum + jj * (NT * 8) + nt * 8);
+                yacc[nt][0] = fmaf(slo, fmaf(d1[nt][0], f1, fmaf(d0[nt][0], f0, zs.x)), yacc[nt][0]);
+                yacc[nt][1] = fmaf(slo, fmaf(d1[nt][1], f1, fmaf(d0[nt][1], f0, zs.y)), yacc[nt][1]);
+                yacc[nt][2] = fmaf(shi, fmaf(d1[nt][2], f1, fmaf(d0[nt][2], f0, zs.x)), yacc[nt][2]);
+                yacc[nt][3] = fmaf(shi, fmaf(d1[nt][3], f1, fmaf(d0[nt][3], f0, zs.y)), yacc[nt][3]);
               }
             }
-        };
-        if (nb == CB) {
-          // full chunk: no per-block branches, so the blocks' instruction streams can interleave
+          } else {
+            float acc[NCH][NT][4];
 #pragma unroll
-          for (int cb = 0; cb < CB; ++cb) do_block(cb);
-        } else {
-          for (int cb = 0; cb < nb; ++cb) do_block(cb);
-        }
-        // the stage has been read into registers by every lane: refill it
+            for (int i = 0; i < 8; ++i) {
+              uint32_t a[4];
+#pragma unroll
+              for (int q = 0; q < 4; ++q) a[q] = field_pair<B>(w, 4 * i + q, 0u);
+#pragma unroll
+              for (int nt = 0; nt < NT; ++nt) {
+                const uint32_t b0 = (i & 1) ? xb[i >> 1][nt].z : xb[i >> 1][nt].x;
+                const uint32_t b1 = (i & 1) ? xb[i >> 1][nt].w : xb[i >> 1][nt].y;
+                if (Chains<B>::first(i))
+                  mma16816<true>(acc[Chains<B>::of(i)][nt], a, b0, b1);
+                else
+                  mma16816<false>(acc[Chains<B>::of(i)][nt], a, b0, b1);
+              }
+            }
+            float slo = 1.f, shi = 1.f;
+            if constexpr (GS == 128) {
+              slo = scale_to_float<BF16>(sblk[0]);
+              shi = scale_to_float<BF16>(sblk[8]);
+            }
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt) {
+              const float2 zs = *reinterpret_cast<const float2 *>(bsum + nt * 8);
+              float tsum[4] = {zs.x, zs.y, zs.x, zs.y};
+#pragma unroll
+              for (int ch = 0; ch < NCH; ++ch)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) tsum[e] = fmaf(acc[ch][nt][e], Chains<B>::inv_factor(ch), tsum[e]);
+              yacc[nt][0] = fmaf(slo, tsum[0], yacc[nt][0]);
+              yacc[nt][1] = fmaf(slo, tsum[1], yacc[nt][1]);
+              yacc[nt][2] = fmaf(shi, tsum[2], yacc[nt][2]);
+              yacc[nt][3] = fmaf(shi, tsum[3], yacc[nt][3]);
+            }
+          }
+      };
+      // after a chunk: the stage has been read into registers by every lane, so it is refilled, and the
+      // consumer moves to the next stage
+      auto advance = [&]() {
+        left -= CB;
+        x_off += CB * 128;
+        z_off += CB * kSumsPerBlock;
         __syncwarp();
-        if (lane == 0 && c + kStages < nchunks) issue_chunk(c + kStages);
+        if (issue_left > 0) issue_next(st_off, st_bar);
+        st_off += kStageBytes;
+        st_bar += 8;
+        if (st_off == kStages * kStageBytes) {
+          st_off = 0;
+          st_bar = bar_full0;
+          st_parity ^= 1;
+        }
+      };
+      for (int cc = 0; cc < full_chunks; ++cc) {
+        if (!mbar_wait(st_bar, st_parity)) {
+          failed = true;
+          break;
+        }
+        // no per-block branches, so the blocks' instruction streams can interleave
+#pragma unroll
+        for (int cb = 0; cb < CB; ++cb) do_block(cb);
+        advance();
       }
+      if (CB > 1 && rem_blocks > 0 && !failed) {
+        if (mbar_wait(st_bar, st_parity)) {
+          for (int cb = 0; cb < rem_blocks; ++cb) do_block(cb);
+          advance();
+        } else {
+          failed = true;
+        }
+      }
+      if (failed) report_status(kStatusWeightCopyTimeout);
     }
     if (xi + 2 < nxst) {
       __syncthreads();  // every warp is done with this activation buffer
@@ -379,15 +423,20 @@ __global__ void __launch_bounds__(256, 2) gemv_kernel(const GemvParams p) {
     }
   }
 
-  if (active) {
-    // 2^(8-b) (exact) and, for one scale per row, the row scale, both in fp32
-    // (csrc/matgptq_gemm.cu:615-633, 943-949), together with 2^24 that undoes the
-    // subnormal encoding of the codes.
-    float mlo = static_cast<float>(1 << (8 - B)) * 16777216.f, mhi = mlo;  // 2^(8-b) and the subnormal scale 2^24
-    if constexpr (GS == -1) {
+  // 2^(8-b) (exact) and, for one scale per row, the row scale, both in fp32
+  // (csrc/matgptq_gemm.cu:615-633, 943-949), together with 2^24 that undoes the
+  // subnormal encoding of the codes.
+  float mlo = static_cast<float>(1 << (8 - B)) * 16777216.f, mhi = mlo;
+  if constexpr (GS == -1) {
+    if (active) {
       mlo *= scale_to_float<BF16>(ldg_u16(p.s + static_cast<size_t>(tile) * 16 + g));
       mhi *= scale_to_float<BF16>(ldg_u16(p.s + static_cast<size_t>(tile) * 16 + g + 8));
     }
+  }
+  const int cols = R * 16;
+  const int n0 = rg * cols;
+  if (S == 1) {
+    // lane (g, t) holds rows g, g+8 of its tile for the batch columns 2t, 2t+1 of every batch tile
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt) {
       red[(nt * 8 + 2 * t + 0) * rstride + warp * 16 + g] = yacc[nt][0] * mlo;
@@ -395,37 +444,51 @@ __global__ void __launch_bounds__(256, 2) gemv_kernel(const GemvParams p) {
       red[(nt * 8 + 2 * t + 0) * rstride + warp * 16 + g + 8] = yacc[nt][2] * mhi;
       red[(nt * 8 + 2 * t + 1) * rstride + warp * 16 + g + 8] = yacc[nt][3] * mhi;
     }
-  } else {
-#pragma unroll
-    for (int nt = 0; nt < NT; ++nt) {
-      red[(nt * 8 + 2 * t + 0) * rstride + warp * 16 + g] = 0.f;
-      red[(nt * 8 + 2 * t + 1) * rstride + warp * 16 + g] = 0.f;
-      red[(nt * 8 + 2 * t + 0) * rstride + warp * 16 + g + 8] = 0.f;
-      red[(nt * 8 + 2 * t + 1) * rstride + warp * 16 + g + 8] = 0.f;
-    }
-  }
-
-  const int cols = R * 16;
-  const int n0 = rg * cols;
-  const int outputs = mvalid * cols;
-  if (S == 1) {
     __syncthreads();
-    for (int idx = threadIdx.x; idx < outputs; idx += blockDim.x) {
-      const int m = idx / cols, n = idx - m * cols;
+    // m = idx / cols through a float product: exact for these small integers (error margin 0.5 / cols)
+    const float inv_cols = 1.f / static_cast<float>(cols);
+    for (int idx = threadIdx.x; idx < mvalid * cols; idx += blockDim.x) {
+      const int m = static_cast<int>((static_cast<float>(idx) + 0.5f) * inv_cols), n = idx - m * cols;
       if (n0 + n < p.N) p.y[static_cast<size_t>(m0 + m) * p.N + n0 + n] = float_to_out<BF16>(red[m * rstride + n]);
     }
   } else {
-    cg::cluster_group cluster = cg::this_cluster();
-    cluster.sync();
-    const int lo = static_cast<int>(static_cast<long long>(crank) * outputs / S);
-    const int hi = static_cast<int>(static_cast<long long>(crank + 1) * outputs / S);
-    for (int idx = lo + threadIdx.x; idx < hi; idx += blockDim.x) {
-      const int m = idx / cols, n = idx - m * cols;
-      float sum = 0.f;
-      for (int r = 0; r < S; ++r) sum += *cluster.map_shared_rank(red + m * rstride + n, r);
-      if (n0 + n < p.N) p.y[static_cast<size_t>(m0 + m) * p.N + n0 + n] = float_to_out<BF16>(sum);
+    // Split-K: CTA r of the cluster owns the columns [r*cw, (r+1)*cw) of this row group.  Every lane
+    // stores its partial sums straight into the owner's shared memory (slot of the sending CTA), one
+    // cluster barrier makes them visible, and the owner adds the S slots in a fixed order.  Nobody
+    // reads remote memory, so a CTA may leave as soon as it has passed the barrier.
+    const int cw = cols >> log2s;
+    const float inv_cw = 1.f / static_cast<float>(cw);
+    const uint32_t red_u32 = smem_base + plan.off_red;
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");  // every peer has started
+    if (active) {
+#pragma unroll
+      for (int hrow = 0; hrow < 2; ++hrow) {
+        const int col = warp * 16 + g + 8 * hrow;
+        const int owner = static_cast<int>((static_cast<float>(col) + 0.5f) * inv_cw);
+        const int j = col - owner * cw;
+        uint32_t remote;
+        asm("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(red_u32 + (crank * plan.xrows * cw + j) * 4), "r"(owner));
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+          for (int e = 0; e < 2; ++e) {
+            const int m = nt * 8 + 2 * t + e;
+            if (m < mvalid)
+              asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote + m * cw * 4),
+                           "f"(yacc[nt][2 * hrow + e] * (hrow ? mhi : mlo))
+                           : "memory");
+          }
+      }
     }
-    cluster.sync();  // peers may still be reading this CTA's partial sums
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+    const int nbase = n0 + crank * cw;
+    for (int idx = threadIdx.x; idx < mvalid * cw; idx += blockDim.x) {
+      const int m = static_cast<int>((static_cast<float>(idx) + 0.5f) * inv_cw), j = idx - m * cw;
+      float sum = 0.f;
+      for (int r = 0; r < S; ++r) sum += red[(r * plan.xrows + m) * cw + j];
+      if (nbase + j < p.N) p.y[static_cast<size_t>(m0 + m) * p.N + nbase + j] = float_to_out<BF16>(sum);
+    }
   }
 }
 
