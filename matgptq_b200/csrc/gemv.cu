@@ -48,15 +48,14 @@ struct GemvParams {
   int tiles;    // N / 16
   int kblocks;  // K / 128
   int split;    // CTAs per cluster along K
+  int stages;   // ring stages per warp
 };
 
-// Blocks per ring stage (1 to 2 KB of packed weights; the blocks of a stage are decoded
-// interleaved) and ring stages per warp (6 to 8 KB in flight per warp).
+// Blocks per ring stage (1.1 to 4.2 KB of packed weights and scales; the blocks of a stage are decoded
+// without a wait or a refill between them).  The number of stages per warp is chosen by the host from
+// the shared memory it wants the CTA to take.
 template <int B> struct ChunkBlocks {
-  static constexpr int value = (B <= 4) ? 2 : 1;
-};
-template <int B> struct Stages {
-  static constexpr int value = (B == 2) ? 6 : (B == 3 || B == 6) ? 5 : 4;
+  static constexpr int value = (B <= 4) ? 4 : 2;
 };
 // blocks (128 in-features each) per activation stage: a multiple of every ChunkBlocks value
 template <int NT> struct XBlocks {
@@ -70,7 +69,7 @@ struct SmemPlan {
 };
 
 template <int B, int GS, int NT>
-__host__ __device__ inline SmemPlan make_plan(int R, int M, int max_nblk) {
+__host__ __device__ inline SmemPlan make_plan(int R, int M, int max_nblk, int stages) {
   SmemPlan p;
   p.xrows = M < NT * 8 ? M : NT * 8;
   const int xb = max_nblk < XBlocks<NT>::value ? max_nblk : XBlocks<NT>::value;
@@ -79,20 +78,20 @@ __host__ __device__ inline SmemPlan make_plan(int R, int M, int max_nblk) {
   p.scale_bytes_per_block = (GS == -1) ? 0 : (GS == 32 ? 128 : 32);
   p.stage_bytes = ChunkBlocks<B>::value * (BlockTraits<B>::WORDS * 4 + p.scale_bytes_per_block);
   p.off_bars = 0;
-  p.off_x = 128 * ((8 * (R * Stages<B>::value + 2) + 127) / 128);
+  p.off_x = 128 * ((8 * (R * stages + 2) + 127) / 128);
   // per activation stage: for every block and group the sum of each activation row (fp32)
   p.sums_per_block = ((GS == 32) ? 4 : 1) * NT * 8;
   p.off_sums = p.off_x + 2 * p.xrows * p.xstride_h * 2;
   p.off_red = p.off_sums + 2 * XBlocks<NT>::value * p.sums_per_block * 4;
   p.off_ring = 128 * ((p.off_red + NT * 8 * p.rstride * 4 + 127) / 128);
-  p.total = p.off_ring + R * Stages<B>::value * p.stage_bytes;
+  p.total = p.off_ring + R * stages * p.stage_bytes;
   return p;
 }
 
 // B: bitwidth, GS: group size (-1, 32, 128), BF16: activation/scale/output type,
 // NT: batch tiles of 8 rows handled per pass.
 template <int B, int GS, bool BF16, int NT>
-__global__ void __launch_bounds__(256, 2) gemv_kernel(const GemvParams p) {
+__global__ void __launch_bounds__(512, 1) gemv_kernel(const GemvParams p) {
   extern __shared__ __align__(128) unsigned char smem_raw[];
 
   const int lane = threadIdx.x & 31;
@@ -114,11 +113,11 @@ __global__ void __launch_bounds__(256, 2) gemv_kernel(const GemvParams p) {
   const int groups = (GS == -1) ? 1 : p.K / GS;
 
   constexpr int CB = ChunkBlocks<B>::value;
-  constexpr int kStages = Stages<B>::value;
+  const int kStages = p.stages;
   constexpr int kXBlocks = XBlocks<NT>::value;
   constexpr int BW = BlockTraits<B>::WORDS;
   constexpr int WBYTES = BW * 4;  // packed bytes per block
-  const SmemPlan plan = make_plan<B, GS, NT>(R, p.M, max_nblk);
+  const SmemPlan plan = make_plan<B, GS, NT>(R, p.M, max_nblk, kStages);
   const uint32_t smem_base = smem_u32(smem_raw);
   const uint32_t bar_full0 = smem_base + plan.off_bars + warp * kStages * 8;  // this warp's ring barriers
   const uint32_t bar_x0 = smem_base + plan.off_bars + R * kStages * 8;        // two activation barriers
@@ -165,9 +164,7 @@ __global__ void __launch_bounds__(256, 2) gemv_kernel(const GemvParams p) {
   };
 
   if (active) {
-#pragma unroll
-    for (int c = 0; c < kStages; ++c)
-      if (c < nchunks) issue_next(c * kStageBytes, bar_full0 + c * 8);
+    for (int c = 0; c < kStages && c < nchunks; ++c) issue_next(c * kStageBytes, bar_full0 + c * 8);
   }
 
   // Everything above reads only weights and scales, which no kernel writes.  The
@@ -497,21 +494,34 @@ __global__ void __launch_bounds__(256, 2) gemv_kernel(const GemvParams p) {
 // ----------------------------------------------------------------------------
 static int g_sm_count = 0;
 
+// Shared memory per CTA that leaves room for exactly `ctas` CTAs on an SM (227 KB usable, 1 KB reserved per CTA).
+static inline int smem_for_ctas_per_sm(int ctas) { return (227 * 1024) / ctas - 1024; }
+
 template <int B, int GS, bool BF16, int NT>
-static int launch_gemv(const GemvParams &p, int R, cudaStream_t stream, bool pdl) {
+static int launch_gemv(GemvParams p, int R, cudaStream_t stream, bool pdl) {
   auto kernel = gemv_kernel<B, GS, BF16, NT>;
   const int S = p.split;
   const int max_nblk = (p.kblocks + S - 1) / S;
-  const SmemPlan plan = make_plan<B, GS, NT>(R, p.M, max_nblk);
-  const size_t smem = static_cast<size_t>(plan.total);
+  // About 16 warps per SM: CTAs of R warps come 16/R to an SM.  The ring takes what is left of that share of
+  // the shared memory after the activations (2 to 8 stages), and the request is padded so that one CTA more
+  // does not fit: the block scheduler otherwise stacks CTAs on the SMs that free up first.
+  const int ctas_per_sm = R >= 16 ? 1 : 16 / R;
+  const int budget = smem_for_ctas_per_sm(ctas_per_sm);
+  const int nchunks = (max_nblk + ChunkBlocks<B>::value - 1) / ChunkBlocks<B>::value;
+  int stages = 2;
+  while (stages < 8 && stages < nchunks && make_plan<B, GS, NT>(R, p.M, max_nblk, stages + 1).total <= budget) ++stages;
+  p.stages = stages;
+  const SmemPlan plan = make_plan<B, GS, NT>(R, p.M, max_nblk, stages);
+  if (plan.total > 227 * 1024 - 1024) return MG_ERR_UNSUPPORTED;
+  const int floor_bytes = smem_for_ctas_per_sm(ctas_per_sm + 1) + 1;
+  const size_t smem = static_cast<size_t>(plan.total > floor_bytes ? plan.total : floor_bytes);
   if (smem > 48 * 1024) {
-    // worst case: 2 x 16 rows x 2112 B of activations + 8 warps x 4 stages x 2.5 KB < 160 KiB: opt in once per device
     static bool opted_in[64] = {};
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess) return MG_ERR_CUDA;
     if (dev < 0 || dev >= 64) return MG_ERR_BAD_ARG;
     if (!opted_in[dev]) {
-      cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
+      cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024);
       if (e != cudaSuccess) return MG_ERR_CUDA;
       opted_in[dev] = true;
     }
@@ -601,7 +611,7 @@ int gemv_launch(int bitwidth, int group_size, int N, int K, int M, const void *w
   gemv_pick_config(p.tiles, p.kblocks, g_sm_count, &R, &S);
   if (R_override > 0) R = R_override;
   if (S_override > 0) S = S_override;
-  if (R < 1 || R > 8 || S < 1 || S > 8 || (S & (S - 1)) != 0 || S > p.kblocks) return MG_ERR_BAD_ARG;
+  if (R < 1 || R > 16 || S < 1 || S > 8 || (S & (S - 1)) != 0 || S > p.kblocks) return MG_ERR_BAD_ARG;
   p.split = S;
   switch (bitwidth) {
     case 2: return launch_gemv_group<2>(p, R, group_size, bf16, stream, pdl);
