@@ -55,8 +55,11 @@ const char *matgptq_b200_strerror(int status);
 int matgptq_b200_matmul(int64_t bitwidth, int64_t group_size, int64_t n_out, int64_t n_in, int64_t batch,
                         const void *w, const void *s, const void *x, void *y, void *stream, uint32_t flags);
 
-/* Same, with the launch shape forced: warps_per_cta in {1..8} row tiles per CTA and
- * split_k in {1,2,4,8} CTAs per cluster along K (0 = choose).  For tuning and tests. */
+/* Same, with the launch shape of the GEMV forced (0 = choose).  For tuning and tests.
+ *   warps_per_cta: low byte = warps per CTA (1..16); next byte = how many of them share one row tile and split
+ *                  the CTA's K range between them (0 or 1 = none; must divide the warps; needs the CTA's whole K
+ *                  slice of the activations in shared memory, else MATGPTQ_B200_ERR_UNSUPPORTED)
+ *   split_k:       CTAs per thread-block cluster along K, one of 1, 2, 4, 8 */
 int matgptq_b200_matmul_tuned(int64_t bitwidth, int64_t group_size, int64_t n_out, int64_t n_in, int64_t batch,
                               const void *w, const void *s, const void *x, void *y, void *stream, uint32_t flags,
                               int warps_per_cta, int split_k);

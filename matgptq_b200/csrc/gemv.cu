@@ -49,6 +49,8 @@ struct GemvParams {
   int kblocks;  // K / 128
   int split;    // CTAs per cluster along K
   int stages;   // ring stages per warp
+  int xblocks;  // blocks (128 in-features) per activation stage: a multiple of ChunkBlocks, or the whole K slice
+  int kslices;  // warps of a CTA that share one row tile and split the CTA's K range (needs the whole slice staged)
 };
 
 // Blocks per ring stage (1.1 to 4.2 KB of packed weights and scales; the blocks of a stage are decoded
@@ -57,11 +59,6 @@ struct GemvParams {
 template <int B> struct ChunkBlocks {
   static constexpr int value = (B <= 4) ? 4 : 2;
 };
-// blocks (128 in-features each) per activation stage: a multiple of every ChunkBlocks value
-template <int NT> struct XBlocks {
-  static constexpr int value = (NT == 1) ? 8 : 4;
-};
-
 // Shared-memory plan of one CTA, computed identically on host and device.
 struct SmemPlan {
   int xrows, xstride_h, rstride, stage_bytes, scale_bytes_per_block, sums_per_block;
@@ -69,10 +66,11 @@ struct SmemPlan {
 };
 
 template <int B, int GS, int NT>
-__host__ __device__ inline SmemPlan make_plan(int R, int M, int max_nblk, int stages) {
+__host__ __device__ inline SmemPlan make_plan(int R, int M, int max_nblk, int stages, int xblocks) {
   SmemPlan p;
   p.xrows = M < NT * 8 ? M : NT * 8;
-  const int xb = max_nblk < XBlocks<NT>::value ? max_nblk : XBlocks<NT>::value;
+  const int xb = max_nblk < xblocks ? max_nblk : xblocks;
+  const int xbufs = xblocks >= max_nblk ? 1 : 2;  // the whole K slice at once needs no second buffer
   p.xstride_h = xb * 128 + 32;  // halves; +64 bytes keeps 16-byte fragment reads conflict free
   p.rstride = R * 16 + 4;
   p.scale_bytes_per_block = (GS == -1) ? 0 : (GS == 32 ? 128 : 32);
@@ -81,8 +79,8 @@ __host__ __device__ inline SmemPlan make_plan(int R, int M, int max_nblk, int st
   p.off_x = 128 * ((8 * (R * stages + 2) + 127) / 128);
   // per activation stage: for every block and group the sum of each activation row (fp32)
   p.sums_per_block = ((GS == 32) ? 4 : 1) * NT * 8;
-  p.off_sums = p.off_x + 2 * p.xrows * p.xstride_h * 2;
-  p.off_red = p.off_sums + 2 * XBlocks<NT>::value * p.sums_per_block * 4;
+  p.off_sums = p.off_x + xbufs * p.xrows * p.xstride_h * 2;
+  p.off_red = p.off_sums + xbufs * xb * p.sums_per_block * 4;
   p.off_ring = 128 * ((p.off_red + NT * 8 * p.rstride * 4 + 127) / 128);
   p.total = p.off_ring + R * stages * p.stage_bytes;
   return p;
@@ -102,11 +100,17 @@ __global__ void __launch_bounds__(512, 1) gemv_kernel(const GemvParams p) {
   const int crank = (S > 1) ? static_cast<int>(cg::this_cluster().block_rank()) : 0;
   const int log2s = 31 - __clz(S);  // S is a power of two (checked by the host)
   const int rg = blockIdx.x >> log2s;
-  const int tile = rg * R + warp;
+  // The CTA's warps form Rt row tiles x RK slices of the CTA's K range.
+  const int RK = p.kslices;
+  const int Rt = R / RK;
+  const int kq = warp / Rt, tw = warp - kq * Rt;
+  const int tile = rg * Rt + tw;
   const bool active = tile < p.tiles;
-  const int kb_lo = (crank * p.kblocks) >> log2s;
+  const int kb_lo = (crank * p.kblocks) >> log2s;  // the CTA's K range, in blocks
   const int kb_hi = ((crank + 1) * p.kblocks) >> log2s;
-  const int nblk = kb_hi - kb_lo;
+  const int nblk_cta = kb_hi - kb_lo;
+  const int w_lo = kq * nblk_cta / RK;  // this warp's part of it, relative to kb_lo
+  const int nblk = (kq + 1) * nblk_cta / RK - w_lo;
   const int max_nblk = (p.kblocks + S - 1) >> log2s;
   const int m0 = blockIdx.y * (NT * 8);
   const int mvalid = min(p.M - m0, NT * 8);
@@ -114,10 +118,10 @@ __global__ void __launch_bounds__(512, 1) gemv_kernel(const GemvParams p) {
 
   constexpr int CB = ChunkBlocks<B>::value;
   const int kStages = p.stages;
-  constexpr int kXBlocks = XBlocks<NT>::value;
+  const int kXBlocks = p.xblocks;
   constexpr int BW = BlockTraits<B>::WORDS;
   constexpr int WBYTES = BW * 4;  // packed bytes per block
-  const SmemPlan plan = make_plan<B, GS, NT>(R, p.M, max_nblk, kStages);
+  const SmemPlan plan = make_plan<B, GS, NT>(R, p.M, max_nblk, kStages, kXBlocks);
   const uint32_t smem_base = smem_u32(smem_raw);
   const uint32_t bar_full0 = smem_base + plan.off_bars + warp * kStages * 8;  // this warp's ring barriers
   const uint32_t bar_x0 = smem_base + plan.off_bars + R * kStages * 8;        // two activation barriers
@@ -125,7 +129,6 @@ __global__ void __launch_bounds__(512, 1) gemv_kernel(const GemvParams p) {
   const unsigned char *ring = smem_raw + plan.off_ring + warp * kStages * plan.stage_bytes;  // this warp's stages
   const uint32_t ring_u32 = smem_base + plan.off_ring + warp * kStages * plan.stage_bytes;
   const int xstride = plan.xstride_h;
-  const int rstride = plan.rstride;
   constexpr int SCB = (GS == -1) ? 0 : (GS == 32 ? 128 : 32);  // scale bytes per block
   constexpr int kStageBytes = CB * (WBYTES + SCB);
 
@@ -144,9 +147,9 @@ __global__ void __launch_bounds__(512, 1) gemv_kernel(const GemvParams p) {
 
   const int nchunks = (nblk + CB - 1) / CB;
   const unsigned char *wsrc = reinterpret_cast<const unsigned char *>(p.w) +
-                              (static_cast<size_t>(active ? tile : 0) * p.kblocks + kb_lo) * WBYTES;
+                              (static_cast<size_t>(active ? tile : 0) * p.kblocks + kb_lo + w_lo) * WBYTES;
   const unsigned char *ssrc = reinterpret_cast<const unsigned char *>(p.s) +
-                              (static_cast<size_t>(active ? tile : 0) * groups) * 32 + static_cast<size_t>(kb_lo) * SCB;
+                              (static_cast<size_t>(active ? tile : 0) * groups) * 32 + static_cast<size_t>(kb_lo + w_lo) * SCB;
 
   // Producer state (used by lane 0): the next chunk to request, as running pointers, so that a refill costs no
   // multiplications.  issue_next() fills the ring stage at byte offset `off` / barrier `bar` with that chunk.
@@ -172,10 +175,10 @@ __global__ void __launch_bounds__(512, 1) gemv_kernel(const GemvParams p) {
   asm volatile("griddepcontrol.launch_dependents;");
   asm volatile("griddepcontrol.wait;" ::: "memory");
 
-  const int nxst = (nblk + kXBlocks - 1) / kXBlocks;
+  const int nxst = (nblk_cta + kXBlocks - 1) / kXBlocks;  // 1 whenever RK > 1
   // thread 0: copy the activations of x stage xi (rows m0.., blocks [xi*kXBlocks, ...)) into buffer xi & 1
   auto issue_x = [&](int xi) {
-    const int nb = min(kXBlocks, nblk - xi * kXBlocks);
+    const int nb = min(kXBlocks, nblk_cta - xi * kXBlocks);
     const uint32_t bar = bar_x0 + (xi & 1) * 8;
     const uint32_t dst = smem_base + plan.off_x + (xi & 1) * plan.xrows * xstride * 2;
     mbar_arrive_expect_tx(bar, mvalid * nb * 256);
@@ -222,7 +225,7 @@ __global__ void __launch_bounds__(512, 1) gemv_kernel(const GemvParams p) {
     }
     uint16_t *xbuf = reinterpret_cast<uint16_t *>(smem_raw + plan.off_x) + (xi & 1) * xbuf_halves;
     float *xsum = sums + (xi & 1) * kXBlocks * kSumsPerBlock;
-    const int st_blocks = min(kXBlocks, nblk - xi * kXBlocks);
+    const int st_blocks = min(kXBlocks, nblk_cta - xi * kXBlocks);
 
     // bf16 activations become fp16 in place (saturating at +-65504): the type the tensor
     // pipe multiplies with the fp16 codes.
@@ -276,8 +279,8 @@ __global__ void __launch_bounds__(512, 1) gemv_kernel(const GemvParams p) {
 
     if (active && !failed) {
       // running offsets inside this activation stage: halves into the x rows, floats into the sums
-      int x_off = (xi & 1) * xbuf_halves;
-      int z_off = (xi & 1) * kXBlocks * kSumsPerBlock;
+      int x_off = (xi & 1) * xbuf_halves + w_lo * 128;  // w_lo is 0 unless the whole slice is staged
+      int z_off = (xi & 1) * kXBlocks * kSumsPerBlock + w_lo * kSumsPerBlock;
       const int stage_blocks = min(kXBlocks, left);
       const int full_chunks = stage_blocks / CB, rem_blocks = stage_blocks - full_chunks * CB;
       auto do_block = [&](int cb) {
@@ -430,60 +433,66 @@ __global__ void __launch_bounds__(512, 1) gemv_kernel(const GemvParams p) {
       mhi *= scale_to_float<BF16>(ldg_u16(p.s + static_cast<size_t>(tile) * 16 + g + 8));
     }
   }
-  const int cols = R * 16;
+  const int cols = Rt * 16;
   const int n0 = rg * cols;
-  if (S == 1) {
-    // lane (g, t) holds rows g, g+8 of its tile for the batch columns 2t, 2t+1 of every batch tile
+  const int nslots = S * RK;  // partial sums per output
+  if (nslots == 1) {
+    // nothing to add up: lane (g, t) holds rows g, g+8 of its tile for the batch columns 2t, 2t+1 of every batch tile
+    if (active) {
 #pragma unroll
-    for (int nt = 0; nt < NT; ++nt) {
-      red[(nt * 8 + 2 * t + 0) * rstride + warp * 16 + g] = yacc[nt][0] * mlo;
-      red[(nt * 8 + 2 * t + 1) * rstride + warp * 16 + g] = yacc[nt][1] * mlo;
-      red[(nt * 8 + 2 * t + 0) * rstride + warp * 16 + g + 8] = yacc[nt][2] * mhi;
-      red[(nt * 8 + 2 * t + 1) * rstride + warp * 16 + g + 8] = yacc[nt][3] * mhi;
-    }
-    __syncthreads();
-    // m = idx / cols through a float product: exact for these small integers (error margin 0.5 / cols)
-    const float inv_cols = 1.f / static_cast<float>(cols);
-    for (int idx = threadIdx.x; idx < mvalid * cols; idx += blockDim.x) {
-      const int m = static_cast<int>((static_cast<float>(idx) + 0.5f) * inv_cols), n = idx - m * cols;
-      if (n0 + n < p.N) p.y[static_cast<size_t>(m0 + m) * p.N + n0 + n] = float_to_out<BF16>(red[m * rstride + n]);
+      for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          const int m = nt * 8 + 2 * t + e;
+          if (m < mvalid) {
+            uint16_t *dst = p.y + static_cast<size_t>(m0 + m) * p.N + n0 + tw * 16 + g;
+            dst[0] = float_to_out<BF16>(yacc[nt][e] * mlo);
+            dst[8] = float_to_out<BF16>(yacc[nt][2 + e] * mhi);
+          }
+        }
     }
   } else {
-    // Split-K: CTA r of the cluster owns the columns [r*cw, (r+1)*cw) of this row group.  Every lane
-    // stores its partial sums straight into the owner's shared memory (slot of the sending CTA), one
-    // cluster barrier makes them visible, and the owner adds the S slots in a fixed order.  Nobody
-    // reads remote memory, so a CTA may leave as soon as it has passed the barrier.
+    // Partial sums: slot (CTA rank, K slice) of the CTA that owns the column.  CTA r of the cluster owns the
+    // columns [r*cw, (r+1)*cw) of this row group.  Every lane stores its partial sums straight into the owner's
+    // shared memory (distributed shared memory when that is a peer), one barrier makes them visible, and the
+    // owner adds the slots in a fixed order.  Nobody reads remote memory, so a CTA may leave as soon as it has
+    // passed the barrier.
     const int cw = cols >> log2s;
     const float inv_cw = 1.f / static_cast<float>(cw);
     const uint32_t red_u32 = smem_base + plan.off_red;
-    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");  // every peer has started
+    const int slot = crank * RK + kq;
+    if (S > 1) asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");  // every peer has started
     if (active) {
 #pragma unroll
       for (int hrow = 0; hrow < 2; ++hrow) {
-        const int col = warp * 16 + g + 8 * hrow;
+        const int col = tw * 16 + g + 8 * hrow;
         const int owner = static_cast<int>((static_cast<float>(col) + 0.5f) * inv_cw);
         const int j = col - owner * cw;
-        uint32_t remote;
-        asm("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(red_u32 + (crank * plan.xrows * cw + j) * 4), "r"(owner));
+        uint32_t dst = red_u32 + (slot * plan.xrows * cw + j) * 4;
+        if (S > 1) asm("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(dst) : "r"(dst), "r"(owner));
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
           for (int e = 0; e < 2; ++e) {
             const int m = nt * 8 + 2 * t + e;
             if (m < mvalid)
-              asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote + m * cw * 4),
+              asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(dst + m * cw * 4),
                            "f"(yacc[nt][2 * hrow + e] * (hrow ? mhi : mlo))
                            : "memory");
           }
       }
     }
-    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
-    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+    if (S > 1) {
+      asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+      asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+    } else {
+      __syncthreads();
+    }
     const int nbase = n0 + crank * cw;
     for (int idx = threadIdx.x; idx < mvalid * cw; idx += blockDim.x) {
       const int m = static_cast<int>((static_cast<float>(idx) + 0.5f) * inv_cw), j = idx - m * cw;
       float sum = 0.f;
-      for (int r = 0; r < S; ++r) sum += red[(r * plan.xrows + m) * cw + j];
+      for (int r = 0; r < nslots; ++r) sum += red[(r * plan.xrows + m) * cw + j];
       if (nbase + j < p.N) p.y[static_cast<size_t>(m0 + m) * p.N + nbase + j] = float_to_out<BF16>(sum);
     }
   }
@@ -508,10 +517,19 @@ static int launch_gemv(GemvParams p, int R, cudaStream_t stream, bool pdl) {
   const int ctas_per_sm = R >= 16 ? 1 : 16 / R;
   const int budget = smem_for_ctas_per_sm(ctas_per_sm);
   const int nchunks = (max_nblk + ChunkBlocks<B>::value - 1) / ChunkBlocks<B>::value;
+  // Activations: the whole K slice of the CTA in one piece when that leaves room for two ring stages (no
+  // buffer turnover, so the warps never meet at a barrier inside the loop), else double-buffered stages.
+  int xblocks = max_nblk;
+  if (make_plan<B, GS, NT>(R, p.M, max_nblk, 2, xblocks).total > budget) {
+    if (p.kslices > 1) return MG_ERR_UNSUPPORTED;  // K slices inside a CTA need the whole slice of the activations staged
+    xblocks = (NT == 1) ? 8 : 4;
+  }
+  if (xblocks > max_nblk) xblocks = max_nblk;
   int stages = 2;
-  while (stages < 8 && stages < nchunks && make_plan<B, GS, NT>(R, p.M, max_nblk, stages + 1).total <= budget) ++stages;
+  while (stages < 8 && stages < nchunks && make_plan<B, GS, NT>(R, p.M, max_nblk, stages + 1, xblocks).total <= budget) ++stages;
   p.stages = stages;
-  const SmemPlan plan = make_plan<B, GS, NT>(R, p.M, max_nblk, stages);
+  p.xblocks = xblocks;
+  const SmemPlan plan = make_plan<B, GS, NT>(R, p.M, max_nblk, stages, xblocks);
   if (plan.total > 227 * 1024 - 1024) return MG_ERR_UNSUPPORTED;
   const int floor_bytes = smem_for_ctas_per_sm(ctas_per_sm + 1) + 1;
   const size_t smem = static_cast<size_t>(plan.total > floor_bytes ? plan.total : floor_bytes);
@@ -526,7 +544,8 @@ static int launch_gemv(GemvParams p, int R, cudaStream_t stream, bool pdl) {
       opted_in[dev] = true;
     }
   }
-  const int row_groups = (p.tiles + R - 1) / R;
+  const int Rt = R / p.kslices;
+  const int row_groups = (p.tiles + Rt - 1) / Rt;
   const int passes = (p.M + NT * 8 - 1) / (NT * 8);
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(row_groups * S, passes, 1);
@@ -575,19 +594,51 @@ static int launch_gemv_group(const GemvParams &p, int R, int group_size, bool bf
   }
 }
 
-// Pick warps per CTA (R) and CTAs per cluster along K (S).  Measured on B200: the
-// kernel wants about 12-14 warps per SM in total (tiles * S close to 2048), S no
-// larger than that needs (every extra CTA pays barrier set-up, an activation copy and
-// the cluster reduction), and R as large as still leaves one CTA per SM, so that the
-// staged activations are shared by many row tiles.
-void gemv_pick_config(int tiles, int kblocks, int sm_count, int *R_out, int *S_out) {
+// Launch shape: R warps per CTA as Rt row tiles x RK slices of the CTA's K range, S CTAs per cluster along K.
+// Measured on B200 (Llama-3-8B shapes, b in {2,4,8}, batch 1/8/16):
+//   * the kernel wants 12-14 warps per SM in total, so K is split T = S * RK ways with tiles * T close to
+//     14 * SMs, and no further (every split pays set-up, an activation copy and the reduction);
+//   * CTAs of 8 warps, two to an SM, beat fatter CTAs for batches up to 8; with more than 8 rows the
+//     activations dominate shared memory and one 16-warp CTA per SM that stages its whole K slice wins;
+//   * for T >= 4 half of the split is better done inside the CTA (RK = 2: partial sums meet in local shared
+//     memory, smaller clusters), provided the CTA's whole K slice of the activations fits (`second` is the
+//     shape to use when it does not).
+struct GemvShape {
+  int R, RK, S;
+};
+
+static void gemv_pick_config(int tiles, int kblocks, int batch, int sm_count, GemvShape *first, GemvShape *second) {
   const int want_warps = 14 * sm_count;
-  int S = 1;
-  while (S < 8 && tiles * S * 2 <= want_warps && S * 2 <= kblocks) S <<= 1;
+  int T = 1;
+  while (T < 16 && tiles * T * 2 <= want_warps && T * 2 <= kblocks) T <<= 1;
+  int S = T > 8 ? 8 : T;
   int R = 8;
   while (R > 1 && static_cast<long long>((tiles + R - 1) / R) * S < sm_count) R >>= 1;
-  *R_out = R;
-  *S_out = S;
+  *second = GemvShape{R, 1, S};
+  *first = *second;
+  if (T >= 4 && tiles >= 4) {
+    *first = GemvShape{8, 2, T / 2};
+  } else if (batch > 8 && T == 2 && tiles >= 16 * sm_count / 4) {
+    *first = GemvShape{16, 1, 2};
+  }
+}
+
+static int launch_shape(GemvParams p, const GemvShape &c, int bitwidth, int group_size, bool bf16, bool pdl,
+                        cudaStream_t stream) {
+  const int R = c.R, S = c.S, RK = c.RK;
+  if (R < 1 || R > 16 || S < 1 || S > 8 || (S & (S - 1)) != 0 || S > p.kblocks) return MG_ERR_BAD_ARG;
+  if (RK < 1 || R % RK != 0 || RK > p.kblocks / S) return MG_ERR_BAD_ARG;
+  if ((R / RK) * 16 % S != 0) return MG_ERR_BAD_ARG;  // the columns of a row group are shared out evenly over the cluster
+  p.split = S;
+  p.kslices = RK;
+  switch (bitwidth) {
+    case 2: return launch_gemv_group<2>(p, R, group_size, bf16, stream, pdl);
+    case 3: return launch_gemv_group<3>(p, R, group_size, bf16, stream, pdl);
+    case 4: return launch_gemv_group<4>(p, R, group_size, bf16, stream, pdl);
+    case 6: return launch_gemv_group<6>(p, R, group_size, bf16, stream, pdl);
+    case 8: return launch_gemv_group<8>(p, R, group_size, bf16, stream, pdl);
+    default: return MG_ERR_BAD_ARG;
+  }
 }
 
 int gemv_launch(int bitwidth, int group_size, int N, int K, int M, const void *w, const void *s, const void *x,
@@ -607,20 +658,23 @@ int gemv_launch(int bitwidth, int group_size, int N, int K, int M, const void *w
   p.M = M;
   p.tiles = N / 16;
   p.kblocks = K / 128;
-  int R, S;
-  gemv_pick_config(p.tiles, p.kblocks, g_sm_count, &R, &S);
-  if (R_override > 0) R = R_override;
-  if (S_override > 0) S = S_override;
-  if (R < 1 || R > 16 || S < 1 || S > 8 || (S & (S - 1)) != 0 || S > p.kblocks) return MG_ERR_BAD_ARG;
-  p.split = S;
-  switch (bitwidth) {
-    case 2: return launch_gemv_group<2>(p, R, group_size, bf16, stream, pdl);
-    case 3: return launch_gemv_group<3>(p, R, group_size, bf16, stream, pdl);
-    case 4: return launch_gemv_group<4>(p, R, group_size, bf16, stream, pdl);
-    case 6: return launch_gemv_group<6>(p, R, group_size, bf16, stream, pdl);
-    case 8: return launch_gemv_group<8>(p, R, group_size, bf16, stream, pdl);
-    default: return MG_ERR_BAD_ARG;
+  GemvShape first, second;
+  gemv_pick_config(p.tiles, p.kblocks, M < 16 ? M : 16, g_sm_count, &first, &second);
+  if (R_override > 0 || S_override > 0) {
+    // forced shape.  warps: low byte = warps per CTA, next byte = K slices inside the CTA (0 means 1)
+    GemvShape forced = second;
+    if (R_override > 0) {
+      forced.R = R_override & 0xFF;
+      forced.RK = (R_override >> 8) & 0xFF;
+      if (forced.RK == 0) forced.RK = 1;
+    }
+    if (S_override > 0) forced.S = S_override;
+    return launch_shape(p, forced, bitwidth, group_size, bf16, pdl, stream);
   }
+  int r = launch_shape(p, first, bitwidth, group_size, bf16, pdl, stream);
+  // Nothing was launched when the shape does not fit in shared memory: use the plain cluster split.
+  if (r == MG_ERR_UNSUPPORTED) r = launch_shape(p, second, bitwidth, group_size, bf16, pdl, stream);
+  return r;
 }
 
 MG_DEFINE_STATUS_ACCESSOR(gemv_device_status)

@@ -14,7 +14,6 @@
 namespace mg {
 
 // gemv.cu
-void gemv_pick_config(int tiles, int kblocks, int sm_count, int *R_out, int *S_out);
 int gemv_launch(int bitwidth, int group_size, int N, int K, int M, const void *w, const void *s, const void *x,
                 void *y, bool bf16, bool pdl, int R_override, int S_override, cudaStream_t stream);
 
