@@ -182,6 +182,27 @@ def build_cells(world: int, rank: int, dev: torch.device):
     return cells
 
 
+_PHASE = ["start"]
+
+
+def progress(msg: str) -> None:
+    """Remember the phase (the watchdog reports it) and, with MATGPTQ_BENCH_VERBOSE=1, print it on stderr."""
+    _PHASE[0] = msg
+    if os.environ.get("MATGPTQ_BENCH_VERBOSE"):
+        print(f"[bench rank {os.environ.get('RANK', '0')}] {msg}", file=sys.stderr, flush=True)
+
+
+def start_watchdog(seconds: float) -> None:
+    """A multi-rank run that stalls (a rank that never joins a collective, a communicator that never comes
+    up) would otherwise sit until somebody kills it: after `seconds` say where it stands and leave."""
+    def bark():
+        time.sleep(seconds)
+        print(f"[bench rank {os.environ.get('RANK', '0')}] watchdog: no result after {seconds:.0f} s, "
+              f"last phase: {_PHASE[0]}", file=sys.stderr, flush=True)
+        os._exit(3)
+    threading.Thread(target=bark, daemon=True).start()
+
+
 def launch_cell(c, flags: int, world: int):
     from matgptq_b200 import ops
     ops.matmul_matgptq_raw(c["x"], c["packed"], c["scales"], c["n_loc"], c["k_loc"], c["b"], GROUP, flags, out=c["y"])
@@ -249,12 +270,17 @@ def ours_main(args) -> None:
     assert torch.cuda.is_available(), "bench.py needs a CUDA device (there is no CPU path)"
     dev = torch.device("cuda", local_rank)
     torch.cuda.set_device(dev)
+    if args.watchdog > 0:
+        start_watchdog(args.watchdog)
     if world > 1:
+        progress("bringing the process group up")
         torch.distributed.init_process_group("nccl", device_id=dev)
     from matgptq_b200 import _native, ops  # noqa: F401
 
     flags = _native.FLAG_ASYNC | (_native.FLAG_PDL if not args.no_pdl else 0)
+    progress("process group up, building cells")
     cells = build_cells(world, rank, dev)
+    progress("cells built")
     step_bytes = sum(c["bytes"] for c in cells)
     launches_per_step = len(cells)
 
@@ -263,10 +289,12 @@ def ours_main(args) -> None:
         for c in cells:  # eager pass: loads kernels, NCCL channels
             launch_cell(c, flags, world)
         stream.synchronize()
+        progress("eager pass done")
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(graph, stream=stream):
             for c in cells:
                 launch_cell(c, flags, world)
+        progress("graph captured")
         sampler = ClockSampler(local_rank)
         if rank == 0:
             sampler.start()
@@ -280,6 +308,7 @@ def ours_main(args) -> None:
             if n_warm % 16 == 0:
                 stream.synchronize()
         stream.synchronize()
+        progress(f"warm-up done ({n_warm} replays)")
         if world > 1:
             torch.distributed.barrier()
         torch.cuda.synchronize()
@@ -293,6 +322,7 @@ def ours_main(args) -> None:
         if world > 1:
             torch.distributed.barrier()
         elapsed_ms = e0.elapsed_time(e1)
+        progress(f"timed steps done: {elapsed_ms:.2f} ms")
         clocks = sampler.stop() if rank == 0 else None
         # a live CUDA graph that holds NCCL kernels blocks the process group's shutdown
         graph.reset()
@@ -316,6 +346,7 @@ def ours_main(args) -> None:
             extra = per_cell_table(dev, flags)
             extra["tensor_core_cells"] = run_tensor_core_cells(dev)
         cpu = run_cpu_arm(steps=2, warmup=1)
+    progress("sweep finished")
     if not args.no_decode:
         # mixed-precision decode, Llama-3.1-8B architecture, mean 3.0 bits, prompt 128, 128 new tokens
         dec = [run_decode(world, rank, dev, "8b", batch, 128, 128, 3.0) for batch in ((1, 8, 32) if world == 1 else (1,))]
@@ -366,11 +397,14 @@ def run_decode(world: int, rank: int, dev: torch.device, model_name: str, batch:
     bits = decode.mixed_bitwidths(shape, mean_bits, seed=0)
     names = decode.layer_names(shape)
     achieved_bits = sum(bits[n] * names[n] for n in names) / sum(names.values())
+    progress(f"decode: building {model_name} batch {batch}")
     model = decode.PackedLlama(shape, bits, dtype=torch.float16, tp_rank=rank, tp_size=world, seed=0, batch=batch,
                                max_seq=prompt_len + new_tokens, device=dev)
+    progress("decode: model built")
     g = torch.Generator().manual_seed(0)
     prompt = torch.randint(0, shape.vocab, (batch, prompt_len), generator=g).to(dev)
     r = model.generate(prompt, new_tokens, use_graph=True)
+    progress("decode: generated")
     t = torch.tensor([r["decode_s"], r["prefill_s"]], device=dev, dtype=torch.float64)
     if world > 1:
         torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
@@ -504,7 +538,10 @@ def decode_main(args) -> None:
     rank = int(os.environ.get("RANK", "0"))
     dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
     torch.cuda.set_device(dev)
+    if args.watchdog > 0:
+        start_watchdog(args.watchdog)
     if world > 1:
+        progress("bringing the process group up")
         torch.distributed.init_process_group("nccl", device_id=dev)
     parts = args.decode.split(":")
     r = run_decode(world, rank, dev, parts[0], int(parts[1]), int(parts[2]), int(parts[3]), float(parts[4]),
@@ -524,6 +561,7 @@ def main() -> None:
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    ap.add_argument("--watchdog", type=float, default=600.0, help="seconds after which a stalled run reports its phase and exits 3 (0 = off)")
     ap.add_argument("--no-pdl", action="store_true", help="launch without programmatic dependent launch")
     ap.add_argument("--no-table", action="store_true", help="skip the per-cell cold-L2 table")
     ap.add_argument("--no-decode", action="store_true", help="skip the whole-model decode measurement")
