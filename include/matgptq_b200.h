@@ -55,6 +55,17 @@ const char *matgptq_b200_strerror(int status);
 int matgptq_b200_matmul(int64_t bitwidth, int64_t group_size, int64_t n_out, int64_t n_in, int64_t batch,
                         const void *w, const void *s, const void *x, void *y, void *stream, uint32_t flags);
 
+/*
+ * Extension (no counterpart in the reference's operator, whose zero point is the implicit 2^(b-1)): the same
+ * product with per-group zero points, Wdq = s * (code * 2^(8-b) - zero), the formula of dequantize()
+ * (src/quant_utils_matgpqt.py:19-22).  `z` holds the zero points in master (8-bit) units, in the type of the
+ * scales and in their reordered layout (matgptq_b200_reorder_scales on the [N, G] zero points).  z == NULL is
+ * matgptq_b200_matmul.  Every batch size runs on the GEMV family (more than 16 rows in passes of 16).
+ */
+int matgptq_b200_matmul_zp(int64_t bitwidth, int64_t group_size, int64_t n_out, int64_t n_in, int64_t batch,
+                           const void *w, const void *s, const void *z, const void *x, void *y, void *stream,
+                           uint32_t flags);
+
 /* Same, with the launch shape of the GEMV forced (0 = choose).  For tuning and tests.
  *   warps_per_cta: low byte = warps per CTA (1..16); next byte = how many of them share one row tile and split
  *                  the CTA's K range between them (0 or 1 = none; must divide the warps; needs the CTA's whole K

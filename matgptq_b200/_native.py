@@ -27,6 +27,7 @@ SIGNATURES = {
     "matgptq_b200_version": (_c_int, []),
     "matgptq_b200_strerror": (ctypes.c_char_p, [_c_int]),
     "matgptq_b200_matmul": (_c_int, [_c_i64, _c_i64, _c_i64, _c_i64, _c_i64, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_u32]),
+    "matgptq_b200_matmul_zp": (_c_int, [_c_i64, _c_i64, _c_i64, _c_i64, _c_i64, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_u32]),
     "matgptq_b200_matmul_tuned": (_c_int, [_c_i64, _c_i64, _c_i64, _c_i64, _c_i64, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_u32, _c_int, _c_int]),
     "matgptq_b200_matmul_ws": (_c_int, [_c_i64, _c_i64, _c_i64, _c_i64, _c_i64, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_u32, _c_ptr, _c_i64, _c_int, _c_int]),
     "matgptq_b200_persistent_gemv_workspace_bytes": (_c_i64, []),

@@ -36,7 +36,7 @@ def should_skip_quantisation(module_name: str) -> bool:
 
 
 def quantization_config(group_size: int, master_bitwidth: int, inference_bitwidth: int, quant_dtype: str,
-                        layer_bitwidths: Mapping[str, int] | None = None) -> dict:
+                        layer_bitwidths: Mapping[str, int] | None = None, zero_points: bool = False) -> dict:
     cfg = {
         "group_size": group_size,
         "modules_to_not_convert": list(EXCLUDED),
@@ -47,6 +47,8 @@ def quantization_config(group_size: int, master_bitwidth: int, inference_bitwidt
     }
     if layer_bitwidths:
         cfg["layer_bitwidths"] = dict(layer_bitwidths)
+    if zero_points:
+        cfg["zero_points"] = True  # the checkpoint holds <layer>.zeros (an addition to the reference's layout)
     return cfg
 
 
@@ -70,7 +72,7 @@ def write_synthetic_checkpoint(out_dir: str, linear_shapes: Mapping[str, tuple],
                                inference_bitwidth: int = 4, quant_dtype: str = "float16",
                                dense_tensors: Mapping[str, torch.Tensor] | None = None,
                                layer_bitwidths: Mapping[str, int] | None = None, base_config: dict | None = None,
-                               seed: int = 0, shard_bytes: int = 2 << 30, device: str = "cpu") -> dict:
+                               seed: int = 0, shard_bytes: int = 2 << 30, device: str = "cpu", sym: bool = True) -> dict:
     """Write a packed checkpoint directory; returns the ``quantization_config`` it wrote."""
     os.makedirs(out_dir, exist_ok=True)
     dtype = {"float16": torch.float16, "bfloat16": torch.bfloat16}[quant_dtype]
@@ -88,9 +90,11 @@ def write_synthetic_checkpoint(out_dir: str, linear_shapes: Mapping[str, tuple],
     for i, (name, (n_out, n_in)) in enumerate(linear_shapes.items()):
         if should_skip_quantisation(name):
             raise ValueError(f"{name} would be skipped by the packer's exclusion rule")
-        layer = synth.make_layer(n_out, n_in, group_size, seed=seed + i, sym=True, dtype=dtype, device=device)
+        layer = synth.make_layer(n_out, n_in, group_size, seed=seed + i, sym=sym, dtype=dtype, device=device)
         put(f"{name}.qweight", layer.qweight)
         put(f"{name}.scales", layer.scales)
+        if not sym:
+            put(f"{name}.zeros", layer.zeros)
     for name, t in (dense_tensors or {}).items():
         put(name, t)
 
@@ -105,7 +109,7 @@ def write_synthetic_checkpoint(out_dir: str, linear_shapes: Mapping[str, tuple],
         with open(os.path.join(out_dir, "model.safetensors.index.json"), "w") as f:
             json.dump({"metadata": {}, "weight_map": weight_map}, f)
 
-    qcfg = quantization_config(group_size, 8, inference_bitwidth, quant_dtype, layer_bitwidths)
+    qcfg = quantization_config(group_size, 8, inference_bitwidth, quant_dtype, layer_bitwidths, zero_points=not sym)
     config = dict(base_config or {})
     config["quantization_config"] = qcfg
     with open(os.path.join(out_dir, "config.json"), "w") as f:
@@ -143,12 +147,18 @@ def iter_checkpoint_tensors(ckpt_dir: str, names: Iterable[str] | None = None):
                     yield key, f.get_tensor(key)
 
 
-def load_linear(ckpt_dir: str, name: str) -> tuple[torch.Tensor, torch.Tensor]:
-    """``(qweight, scales)`` of one quantised linear layer."""
-    got = dict(iter_checkpoint_tensors(ckpt_dir, [f"{name}.qweight", f"{name}.scales"]))
-    if len(got) != 2:
+def load_linear(ckpt_dir: str, name: str, with_zeros: bool = False):
+    """``(qweight, scales)`` of one quantised linear layer, or ``(qweight, scales, zeros)`` with ``with_zeros``
+    (``zeros`` is None when the checkpoint has none: implicit zero point 128)."""
+    got = dict(iter_checkpoint_tensors(ckpt_dir, [f"{name}.qweight", f"{name}.scales", f"{name}.zeros"]))
+    if f"{name}.qweight" not in got or f"{name}.scales" not in got:
         raise KeyError(f"{name}: qweight/scales not found in {ckpt_dir}")
     q, s = got[f"{name}.qweight"], got[f"{name}.scales"]
     if q.dtype != torch.uint8 or q.dim() != 2 or s.dim() != 2 or s.shape[0] != q.shape[0]:
         raise ValueError(f"{name}: unexpected tensor layout {q.dtype}{tuple(q.shape)} / {s.dtype}{tuple(s.shape)}")
-    return q, s
+    if not with_zeros:
+        return q, s
+    z = got.get(f"{name}.zeros")
+    if z is not None and (z.shape != s.shape or z.dtype != s.dtype):
+        raise ValueError(f"{name}: zeros {z.dtype}{tuple(z.shape)} do not match scales {s.dtype}{tuple(s.shape)}")
+    return q, s, z

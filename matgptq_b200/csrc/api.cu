@@ -55,13 +55,13 @@ static int sm_count_of_current_device(int *out) {
 
 static int matmul_impl(int64_t bitwidth, int64_t group_size, int64_t n_out, int64_t n_in, int64_t batch, const void *w,
                        const void *s, const void *x, void *y, void *stream, uint32_t flags, void *workspace,
-                       int64_t workspace_bytes, int path, int warps_per_cta, int split_k) {
+                       int64_t workspace_bytes, int path, int warps_per_cta, int split_k, const void *z = nullptr) {
   const int st = check_shape(n_out, n_in, bitwidth, group_size);
   if (st != MG_OK) return st;
   if (batch < 0 || batch > (1 << 24) || path < 0 || path > 3 || workspace_bytes < 0) return MG_ERR_BAD_ARG;
   if (batch == 0) return MG_OK;
   if (!w || !s || !x || !y) return MG_ERR_BAD_ARG;
-  if (!aligned16(w) || !aligned16(x) || !aligned16(s) || (reinterpret_cast<uintptr_t>(y) & 1u) ||
+  if (!aligned16(w) || !aligned16(x) || !aligned16(s) || !aligned16(z) || (reinterpret_cast<uintptr_t>(y) & 1u) ||
       (workspace && !aligned16(workspace)))
     return MG_ERR_ALIGNMENT;
   cudaStream_t cs = static_cast<cudaStream_t>(stream);
@@ -69,7 +69,13 @@ static int matmul_impl(int64_t bitwidth, int64_t group_size, int64_t n_out, int6
   const bool pdl = (flags & MATGPTQ_B200_FLAG_PDL) != 0;
   const bool tensor_core = path == 2 || (path == 0 && batch >= kTensorCoreMinBatch);
   int r;
-  if (tensor_core) {
+  if (z) {
+    // zero points: every batch size runs on the GEMV family (more than 16 rows in passes of 16); the tensor-core
+    // path and the persistent kernel have the implicit zero point only
+    if (path > 1) return MG_ERR_UNSUPPORTED;
+    r = mg::gemv_zp_launch(static_cast<int>(bitwidth), static_cast<int>(group_size), static_cast<int>(n_out),
+                           static_cast<int>(n_in), static_cast<int>(batch), w, s, z, x, y, bf16, pdl, warps_per_cta, split_k, cs);
+  } else if (tensor_core) {
     r = mg::gemm_tc_launch(static_cast<int>(bitwidth), static_cast<int>(group_size), static_cast<int>(n_out),
                            static_cast<int>(n_in), static_cast<int>(batch), w, s, x, y, workspace, workspace_bytes, bf16,
                            pdl, split_k, cs);
@@ -84,7 +90,7 @@ static int matmul_impl(int64_t bitwidth, int64_t group_size, int64_t n_out, int6
                                  bf16, pdl, cs);
     if (r == MG_ERR_UNSUPPORTED && path != 3)
       r = mg::gemv_launch(static_cast<int>(bitwidth), static_cast<int>(group_size), static_cast<int>(n_out),
-                          static_cast<int>(n_in), static_cast<int>(batch), w, s, x, y, bf16, pdl, warps_per_cta, split_k, cs);
+                          static_cast<int>(n_in), static_cast<int>(batch), w, s, nullptr, x, y, bf16, pdl, warps_per_cta, split_k, cs);
   }
   if (r != MG_OK) return r;
   if (!(flags & MATGPTQ_B200_FLAG_ASYNC)) {
@@ -104,6 +110,12 @@ int matgptq_b200_matmul_tuned(int64_t bitwidth, int64_t group_size, int64_t n_ou
 int matgptq_b200_matmul(int64_t bitwidth, int64_t group_size, int64_t n_out, int64_t n_in, int64_t batch,
                         const void *w, const void *s, const void *x, void *y, void *stream, uint32_t flags) {
   return matmul_impl(bitwidth, group_size, n_out, n_in, batch, w, s, x, y, stream, flags, nullptr, 0, 0, 0, 0);
+}
+
+int matgptq_b200_matmul_zp(int64_t bitwidth, int64_t group_size, int64_t n_out, int64_t n_in, int64_t batch,
+                           const void *w, const void *s, const void *z, const void *x, void *y, void *stream,
+                           uint32_t flags) {
+  return matmul_impl(bitwidth, group_size, n_out, n_in, batch, w, s, x, y, stream, flags, nullptr, 0, 0, 0, 0, z);
 }
 
 int matgptq_b200_matmul_ws(int64_t bitwidth, int64_t group_size, int64_t n_out, int64_t n_in, int64_t batch,
@@ -200,10 +212,12 @@ int matgptq_b200_device_status(int *status_out, int reset) {
   if (r != MG_OK) return r;
   r = mg::gemm_tc_device_status(&b, reset);
   if (r != MG_OK) return r;
-  int c = 0;
+  int c = 0, d = 0;
   r = mg::gemv_stream_device_status(&c, reset);
   if (r != MG_OK) return r;
-  if (status_out) *status_out = a ? a : (b ? b : c);
+  r = mg::gemv_zp_device_status(&d, reset);
+  if (r != MG_OK) return r;
+  if (status_out) *status_out = a ? a : (b ? b : (c ? c : d));
   return MG_OK;
 }
 

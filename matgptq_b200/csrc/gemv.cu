@@ -37,11 +37,21 @@
 
 namespace cg = cooperative_groups;
 
+// This file is compiled twice: as it is (implicit zero point 2^(b-1), what the reference's operator computes)
+// and from gemv_zp.cu with MG_GEMV_ZP = 1 (per-group zero points, an extension).  Everything that differs
+// between the two carries kZP in its template arguments or its name, so the two objects link together.
+#ifndef MG_GEMV_ZP
+#define MG_GEMV_ZP 0
+#endif
+
 namespace mg {
+
+constexpr bool kZP = MG_GEMV_ZP != 0;
 
 struct GemvParams {
   const uint32_t *w;
   const uint16_t *s;
+  const uint16_t *z;  // zero points in master units, laid out like the scales (only read when kZP)
   const uint16_t *x;
   uint16_t *y;
   int N, K, M;
@@ -56,7 +66,9 @@ struct GemvParams {
 // Blocks per ring stage (1.1 to 4.2 KB of packed weights and scales; the blocks of a stage are decoded
 // without a wait or a refill between them).  The number of stages per warp is chosen by the host from
 // the shared memory it wants the CTA to take.
-template <int B> struct ChunkBlocks {
+template <int B, int NT> struct ChunkBlocks {
+  // (two-block stages for two batch tiles were tried: the whole-slice staging then fits for down at b <= 4,
+  // batch 16 (-14 %), but every other batch-16 cell loses 2-5 % to the extra waits; net zero)
   static constexpr int value = (B <= 4) ? 4 : 2;
 };
 // Shared-memory plan of one CTA, computed identically on host and device.
@@ -65,7 +77,7 @@ struct SmemPlan {
   int off_bars, off_x, off_sums, off_red, off_ring, total;
 };
 
-template <int B, int GS, int NT>
+template <int B, int GS, int NT, bool ZP>
 __host__ __device__ inline SmemPlan make_plan(int R, int M, int max_nblk, int stages, int xblocks) {
   SmemPlan p;
   p.xrows = M < NT * 8 ? M : NT * 8;
@@ -74,7 +86,7 @@ __host__ __device__ inline SmemPlan make_plan(int R, int M, int max_nblk, int st
   p.xstride_h = xb * 128 + 32;  // halves; +64 bytes keeps 16-byte fragment reads conflict free
   p.rstride = R * 16 + 4;
   p.scale_bytes_per_block = (GS == -1) ? 0 : (GS == 32 ? 128 : 32);
-  p.stage_bytes = ChunkBlocks<B>::value * (BlockTraits<B>::WORDS * 4 + p.scale_bytes_per_block);
+  p.stage_bytes = ChunkBlocks<B, NT>::value * (BlockTraits<B>::WORDS * 4 + p.scale_bytes_per_block * (ZP ? 2 : 1));
   p.off_bars = 0;
   p.off_x = 128 * ((8 * (R * stages + 2) + 127) / 128);
   // per activation stage: for every block and group the sum of each activation row (fp32)
@@ -88,7 +100,7 @@ __host__ __device__ inline SmemPlan make_plan(int R, int M, int max_nblk, int st
 
 // B: bitwidth, GS: group size (-1, 32, 128), BF16: activation/scale/output type,
 // NT: batch tiles of 8 rows handled per pass.
-template <int B, int GS, bool BF16, int NT>
+template <int B, int GS, bool BF16, int NT, bool ZP>
 __global__ void __launch_bounds__(512, 1) gemv_kernel(const GemvParams p) {
   extern __shared__ __align__(128) unsigned char smem_raw[];
 
@@ -116,12 +128,12 @@ __global__ void __launch_bounds__(512, 1) gemv_kernel(const GemvParams p) {
   const int mvalid = min(p.M - m0, NT * 8);
   const int groups = (GS == -1) ? 1 : p.K / GS;
 
-  constexpr int CB = ChunkBlocks<B>::value;
+  constexpr int CB = ChunkBlocks<B, NT>::value;
   const int kStages = p.stages;
   const int kXBlocks = p.xblocks;
   constexpr int BW = BlockTraits<B>::WORDS;
   constexpr int WBYTES = BW * 4;  // packed bytes per block
-  const SmemPlan plan = make_plan<B, GS, NT>(R, p.M, max_nblk, kStages, kXBlocks);
+  const SmemPlan plan = make_plan<B, GS, NT, kZP>(R, p.M, max_nblk, kStages, kXBlocks);
   const uint32_t smem_base = smem_u32(smem_raw);
   const uint32_t bar_full0 = smem_base + plan.off_bars + warp * kStages * 8;  // this warp's ring barriers
   const uint32_t bar_x0 = smem_base + plan.off_bars + R * kStages * 8;        // two activation barriers
@@ -130,7 +142,7 @@ __global__ void __launch_bounds__(512, 1) gemv_kernel(const GemvParams p) {
   const uint32_t ring_u32 = smem_base + plan.off_ring + warp * kStages * plan.stage_bytes;
   const int xstride = plan.xstride_h;
   constexpr int SCB = (GS == -1) ? 0 : (GS == 32 ? 128 : 32);  // scale bytes per block
-  constexpr int kStageBytes = CB * (WBYTES + SCB);
+  constexpr int kStageBytes = CB * (WBYTES + SCB * (ZP ? 2 : 1));
 
   if (lane == 0) {
     for (int i = 0; i < kStages; ++i) mbar_init(bar_full0 + i * 8, 1);
@@ -151,18 +163,23 @@ __global__ void __launch_bounds__(512, 1) gemv_kernel(const GemvParams p) {
   const unsigned char *ssrc = reinterpret_cast<const unsigned char *>(p.s) +
                               (static_cast<size_t>(active ? tile : 0) * groups) * 32 + static_cast<size_t>(kb_lo + w_lo) * SCB;
 
+  const unsigned char *zsrc = reinterpret_cast<const unsigned char *>(p.z) +
+                              (static_cast<size_t>(active ? tile : 0) * groups) * 32 + static_cast<size_t>(kb_lo + w_lo) * SCB;
+
   // Producer state (used by lane 0): the next chunk to request, as running pointers, so that a refill costs no
   // multiplications.  issue_next() fills the ring stage at byte offset `off` / barrier `bar` with that chunk.
   int issue_left = nblk;  // blocks not requested yet
   auto issue_next = [&](uint32_t off, uint32_t bar) {  // called by every lane; lane 0 issues the copies
     const int nb = min(CB, issue_left);
     if (lane == 0) {
-      mbar_arrive_expect_tx(bar, nb * (WBYTES + SCB));
+      mbar_arrive_expect_tx(bar, nb * (WBYTES + SCB * (ZP ? 2 : 1)));
       bulk_copy_g2s(ring_u32 + off, wsrc, nb * WBYTES, bar);
       if (GS != -1) bulk_copy_g2s(ring_u32 + off + CB * WBYTES, ssrc, nb * SCB, bar);
+      if (GS != -1 && ZP) bulk_copy_g2s(ring_u32 + off + CB * (WBYTES + SCB), zsrc, nb * SCB, bar);
     }
     wsrc += CB * WBYTES;
     ssrc += CB * SCB;
+    zsrc += CB * SCB;
     issue_left -= CB;
   };
 
@@ -198,13 +215,24 @@ __global__ void __launch_bounds__(512, 1) gemv_kernel(const GemvParams p) {
     for (int e = 0; e < 4; ++e) yacc[nt][e] = 0.f;
 
   constexpr int NCH = Chains<B>::N;
-  constexpr float kNegZero = -static_cast<float>(BlockTraits<B>::ZERO) * 5.9604644775390625e-08f;  // -Z * 2^-24
+  // factor of the activation row sums: -Z * 2^-24 with the implicit zero point Z = 2^(b-1); with zero points
+  // -2^-24, and the zero point of the row and group (in code units: master units / 2^(8-b)) multiplies later
+  constexpr float kNegZero = -(ZP ? 1.f : static_cast<float>(BlockTraits<B>::ZERO)) * 5.9604644775390625e-08f;
+  constexpr float kZeroToCode = 1.f / static_cast<float>(1 << (8 - B));
+  float zrow_lo = 1.f, zrow_hi = 1.f;  // one zero point per row (GS == -1)
+  if constexpr (ZP && GS == -1) {
+    if (active) {
+      zrow_lo = kZeroToCode * scale_to_float<BF16>(ldg_u16(p.z + static_cast<size_t>(tile) * 16 + g));
+      zrow_hi = kZeroToCode * scale_to_float<BF16>(ldg_u16(p.z + static_cast<size_t>(tile) * 16 + g + 8));
+    }
+  }
   float *sums = reinterpret_cast<float *>(smem_raw + plan.off_sums);
 
   // Loop-invariant per-lane addresses: everything inside the block loop is base + running offset + constant.
   const unsigned char *w_lane = ring + lane * 16;                        // 16-byte vectors of the packed words
   const unsigned char *w_tail = ring + BlockTraits<B>::NV * 512 + lane * 8;  // the 8-byte tail (3-bit blocks)
   const unsigned char *s_lane = ring + CB * WBYTES + g * 2;              // scales of rows g and g+8
+  const unsigned char *zp_lane = s_lane + CB * SCB;                      // their zero points (kZP)
   const uint16_t *x_lane[NT];
 #pragma unroll
   for (int nt = 0; nt < NT; ++nt)
@@ -303,6 +331,7 @@ __global__ void __launch_bounds__(512, 1) gemv_kernel(const GemvParams p) {
           }
           const uint16_t *sblk = reinterpret_cast<const uint16_t *>(s_lane + st_off + cb * SCB);  // [0]: row g, [8]: row g+8
           const float *bsum = z_lane + z_off + cb * kSumsPerBlock;
+          const uint16_t *zblk = reinterpret_cast<const uint16_t *>(zp_lane + st_off + cb * SCB);
 
           // lanes whose batch column does not exist read the last valid row: their
           // accumulator columns are never written out
@@ -334,10 +363,19 @@ __global__ void __launch_bounds__(512, 1) gemv_kernel(const GemvParams p) {
                 mma16816<true>(d0[nt], a0, xb[jj][nt].x, xb[jj][nt].y);
                 mma16816<true>(d1[nt], a1, xb[jj][nt].z, xb[jj][nt].w);
                 const float2 zs = *reinterpret_cast<const float2 *>(bsum + jj * (NT * 8) + nt * 8);
-                yacc[nt][0] = fmaf(slo, fmaf(d1[nt][0], f1, fmaf(d0[nt][0], f0, zs.x)), yacc[nt][0]);
-                yacc[nt][1] = fmaf(slo, fmaf(d1[nt][1], f1, fmaf(d0[nt][1], f0, zs.y)), yacc[nt][1]);
-                yacc[nt][2] = fmaf(shi, fmaf(d1[nt][2], f1, fmaf(d0[nt][2], f0, zs.x)), yacc[nt][2]);
-                yacc[nt][3] = fmaf(shi, fmaf(d1[nt][3], f1, fmaf(d0[nt][3], f0, zs.y)), yacc[nt][3]);
+                float z4[4] = {zs.x, zs.y, zs.x, zs.y};
+                if constexpr (ZP) {
+                  const float zl = kZeroToCode * scale_to_float<BF16>(zblk[jj * 16]);
+                  const float zh = kZeroToCode * scale_to_float<BF16>(zblk[jj * 16 + 8]);
+                  z4[0] *= zl;
+                  z4[1] *= zl;
+                  z4[2] *= zh;
+                  z4[3] *= zh;
+                }
+                yacc[nt][0] = fmaf(slo, fmaf(d1[nt][0], f1, fmaf(d0[nt][0], f0, z4[0])), yacc[nt][0]);
+                yacc[nt][1] = fmaf(slo, fmaf(d1[nt][1], f1, fmaf(d0[nt][1], f0, z4[1])), yacc[nt][1]);
+                yacc[nt][2] = fmaf(shi, fmaf(d1[nt][2], f1, fmaf(d0[nt][2], f0, z4[2])), yacc[nt][2]);
+                yacc[nt][3] = fmaf(shi, fmaf(d1[nt][3], f1, fmaf(d0[nt][3], f0, z4[3])), yacc[nt][3]);
               }
             }
           } else {
@@ -366,6 +404,17 @@ __global__ void __launch_bounds__(512, 1) gemv_kernel(const GemvParams p) {
             for (int nt = 0; nt < NT; ++nt) {
               const float2 zs = *reinterpret_cast<const float2 *>(bsum + nt * 8);
               float tsum[4] = {zs.x, zs.y, zs.x, zs.y};
+              if constexpr (ZP) {
+                float zl = zrow_lo, zh = zrow_hi;
+                if constexpr (GS == 128) {
+                  zl = kZeroToCode * scale_to_float<BF16>(zblk[0]);
+                  zh = kZeroToCode * scale_to_float<BF16>(zblk[8]);
+                }
+                tsum[0] *= zl;
+                tsum[1] *= zl;
+                tsum[2] *= zh;
+                tsum[3] *= zh;
+              }
 #pragma unroll
               for (int ch = 0; ch < NCH; ++ch)
 #pragma unroll
@@ -508,7 +557,7 @@ static inline int smem_for_ctas_per_sm(int ctas) { return (227 * 1024) / ctas - 
 
 template <int B, int GS, bool BF16, int NT>
 static int launch_gemv(GemvParams p, int R, cudaStream_t stream, bool pdl) {
-  auto kernel = gemv_kernel<B, GS, BF16, NT>;
+  auto kernel = gemv_kernel<B, GS, BF16, NT, kZP>;
   const int S = p.split;
   const int max_nblk = (p.kblocks + S - 1) / S;
   // About 16 warps per SM: CTAs of R warps come 16/R to an SM.  The ring takes what is left of that share of
@@ -516,20 +565,20 @@ static int launch_gemv(GemvParams p, int R, cudaStream_t stream, bool pdl) {
   // does not fit: the block scheduler otherwise stacks CTAs on the SMs that free up first.
   const int ctas_per_sm = R >= 16 ? 1 : 16 / R;
   const int budget = smem_for_ctas_per_sm(ctas_per_sm);
-  const int nchunks = (max_nblk + ChunkBlocks<B>::value - 1) / ChunkBlocks<B>::value;
+  const int nchunks = (max_nblk + ChunkBlocks<B, NT>::value - 1) / ChunkBlocks<B, NT>::value;
   // Activations: the whole K slice of the CTA in one piece when that leaves room for two ring stages (no
   // buffer turnover, so the warps never meet at a barrier inside the loop), else double-buffered stages.
   int xblocks = max_nblk;
-  if (make_plan<B, GS, NT>(R, p.M, max_nblk, 2, xblocks).total > budget) {
+  if (make_plan<B, GS, NT, kZP>(R, p.M, max_nblk, 2, xblocks).total > budget) {
     if (p.kslices > 1) return MG_ERR_UNSUPPORTED;  // K slices inside a CTA need the whole slice of the activations staged
     xblocks = (NT == 1) ? 8 : 4;
   }
   if (xblocks > max_nblk) xblocks = max_nblk;
   int stages = 2;
-  while (stages < 8 && stages < nchunks && make_plan<B, GS, NT>(R, p.M, max_nblk, stages + 1, xblocks).total <= budget) ++stages;
+  while (stages < 8 && stages < nchunks && make_plan<B, GS, NT, kZP>(R, p.M, max_nblk, stages + 1, xblocks).total <= budget) ++stages;
   p.stages = stages;
   p.xblocks = xblocks;
-  const SmemPlan plan = make_plan<B, GS, NT>(R, p.M, max_nblk, stages, xblocks);
+  const SmemPlan plan = make_plan<B, GS, NT, kZP>(R, p.M, max_nblk, stages, xblocks);
   if (plan.total > 227 * 1024 - 1024) return MG_ERR_UNSUPPORTED;
   const int floor_bytes = smem_for_ctas_per_sm(ctas_per_sm + 1) + 1;
   const size_t smem = static_cast<size_t>(plan.total > floor_bytes ? plan.total : floor_bytes);
@@ -641,8 +690,18 @@ static int launch_shape(GemvParams p, const GemvShape &c, int bitwidth, int grou
   }
 }
 
-int gemv_launch(int bitwidth, int group_size, int N, int K, int M, const void *w, const void *s, const void *x,
-                void *y, bool bf16, bool pdl, int R_override, int S_override, cudaStream_t stream) {
+#if MG_GEMV_ZP
+#define MG_GEMV_LAUNCH gemv_zp_launch
+#define MG_GEMV_STATUS gemv_zp_device_status
+#else
+#define MG_GEMV_LAUNCH gemv_launch
+#define MG_GEMV_STATUS gemv_device_status
+#endif
+
+// z: zero points (reordered like the scales) for the build with zero points, null for the other one
+int MG_GEMV_LAUNCH(int bitwidth, int group_size, int N, int K, int M, const void *w, const void *s, const void *z,
+                   const void *x, void *y, bool bf16, bool pdl, int R_override, int S_override, cudaStream_t stream) {
+  if (kZP != (z != nullptr)) return MG_ERR_BAD_ARG;
   if (g_sm_count == 0) {
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess) return MG_ERR_CUDA;
@@ -651,6 +710,7 @@ int gemv_launch(int bitwidth, int group_size, int N, int K, int M, const void *w
   GemvParams p;
   p.w = static_cast<const uint32_t *>(w);
   p.s = static_cast<const uint16_t *>(s);
+  p.z = static_cast<const uint16_t *>(z);
   p.x = static_cast<const uint16_t *>(x);
   p.y = static_cast<uint16_t *>(y);
   p.N = N;
@@ -677,6 +737,6 @@ int gemv_launch(int bitwidth, int group_size, int N, int K, int M, const void *w
   return r;
 }
 
-MG_DEFINE_STATUS_ACCESSOR(gemv_device_status)
+MG_DEFINE_STATUS_ACCESSOR(MG_GEMV_STATUS)
 
 }  // namespace mg

@@ -14,10 +14,14 @@
 namespace mg {
 
 // gemv.cu
-int gemv_launch(int bitwidth, int group_size, int N, int K, int M, const void *w, const void *s, const void *x,
-                void *y, bool bf16, bool pdl, int R_override, int S_override, cudaStream_t stream);
+// z must be null for gemv_launch and non-null for gemv_zp_launch (gemv_zp.cu: the same kernels with zero points)
+int gemv_launch(int bitwidth, int group_size, int N, int K, int M, const void *w, const void *s, const void *z,
+                const void *x, void *y, bool bf16, bool pdl, int R_override, int S_override, cudaStream_t stream);
+int gemv_zp_launch(int bitwidth, int group_size, int N, int K, int M, const void *w, const void *s, const void *z,
+                   const void *x, void *y, bool bf16, bool pdl, int R_override, int S_override, cudaStream_t stream);
 
 int gemv_device_status(int *status_out, int reset);
+int gemv_zp_device_status(int *status_out, int reset);
 
 // gemv_stream.cu
 long long gemv_stream_workspace_bytes(int sm_count);

@@ -209,6 +209,55 @@ def _matmul_fake(input, matgptq_weights, matgptq_scales, n_out_features, n_in_fe
                            dtype=torch.bfloat16 if feature_flag & 2 else torch.float16)
 
 
+@torch.library.custom_op("matgptq_cuda::matmul_matgptq_zeros", mutates_args=())
+def matmul_matgptq_zeros(
+    input: torch.Tensor,
+    matgptq_weights: torch.Tensor,
+    matgptq_scales: torch.Tensor,
+    matgptq_zeros: torch.Tensor,
+    n_out_features: int,
+    n_in_features: int,
+    bitwidth: int,
+    group_size: int,
+    feature_flag: int,
+) -> torch.Tensor:
+    """Extension: ``matmul_matgptq`` with per-group zero points, ``Wdq = s * (code * 2^(8-b) - zero)`` as in the
+    reference's ``dequantize`` (``src/quant_utils_matgpqt.py:19-22``).  ``matgptq_zeros`` are the zero points in
+    master (8-bit) units, in the dtype of the scales, passed through ``reorder_matgptq_scales`` like the scales.
+    The reference's operator has no such argument (its zero point is the implicit ``2^(b-1)``)."""
+    _check_matmul_args(input, matgptq_weights, matgptq_scales, n_out_features, n_in_features, bitwidth, group_size)
+    bf16 = bool(feature_flag & _native.FLAG_BF16)
+    dtype = torch.bfloat16 if bf16 else torch.float16
+    if input.dtype != dtype or matgptq_scales.dtype != dtype or matgptq_zeros.dtype != dtype:
+        raise RuntimeError(f"input, matgptq_scales and matgptq_zeros must be {dtype} for feature_flag={feature_flag}")
+    if matgptq_zeros.shape != matgptq_scales.shape or matgptq_zeros.device != matgptq_scales.device:
+        raise RuntimeError("matgptq_zeros must have the shape and device of matgptq_scales")
+    dev = matgptq_weights.device
+    batch = input.size(-2)
+    x = input
+    if input.dim() > 2:
+        x = input.reshape(-1, batch, n_in_features)[0]
+    if not x.is_contiguous():
+        x = x.contiguous()
+    if x.data_ptr() % 16 != 0:
+        x = x.clone()
+    z = matgptq_zeros.contiguous()
+    with torch.cuda.device(dev):
+        out = torch.empty((batch, n_out_features), dtype=dtype, device=dev)
+        st = _lib.matgptq_b200_matmul_zp(bitwidth, group_size, n_out_features, n_in_features, batch,
+                                         matgptq_weights.data_ptr(), matgptq_scales.data_ptr(), z.data_ptr(),
+                                         x.data_ptr(), out.data_ptr(), _stream_ptr(dev), feature_flag)
+        _native.check(st, "matmul_matgptq_zeros")
+    return out
+
+
+@matmul_matgptq_zeros.register_fake
+def _matmul_zeros_fake(input, matgptq_weights, matgptq_scales, matgptq_zeros, n_out_features, n_in_features, bitwidth,
+                       group_size, feature_flag):
+    return input.new_empty((input.shape[-2], n_out_features),
+                           dtype=torch.bfloat16 if feature_flag & 2 else torch.float16)
+
+
 @torch.library.custom_op("matgptq_cuda::dequantize_matgptq", mutates_args=())
 def dequantize_matgptq(
     matgptq_weights: torch.Tensor,

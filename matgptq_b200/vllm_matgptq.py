@@ -12,6 +12,9 @@ Additions (absent keys give the reference's behaviour):
     (``inference_lib/inference_demo_transformers.py:45-49``).  vLLM fuses q/k/v and gate/up into one
     layer, so a fused layer may carry several bitwidths: each output partition is packed and run at
     its own bitwidth.
+  * ``zero_points`` (bool): the checkpoint also holds ``<layer>.zeros`` (``[N, K/g]``, master units, dtype of
+    the scales; ``dequantize`` of ``src/quant_utils_matgpqt.py:19-22`` takes them, the reference's operator and
+    packer do not).  The layers then run ``matmul_matgptq_zeros``.
   * slicing is fused into packing on the GPU (the reference slices with torch ops and packs on one
     CPU thread, ``vllm_matgptq.py:150-166``, ``csrc/bindings.cpp:63-83``).
 """
@@ -42,6 +45,7 @@ class MatGPTQConfig(QuantizationConfig):
         quant_dtype: str = "float16",
         modules_to_not_convert: list[str] | None = None,
         layer_bitwidths: dict[str, int] | None = None,
+        zero_points: bool = False,
     ) -> None:
         super().__init__()
         assert group_size in [-1, 32, 128]
@@ -52,6 +56,7 @@ class MatGPTQConfig(QuantizationConfig):
         self.quant_dtype = {"float16": torch.float16, "bfloat16": torch.bfloat16}[quant_dtype]
         self.modules_to_not_convert = modules_to_not_convert
         self.layer_bitwidths = dict(layer_bitwidths) if layer_bitwidths else None
+        self.zero_points = bool(zero_points)
         self.flag = MatGTPQ_FeatureFlags.ASYNC + MatGTPQ_FeatureFlags.IS_BF16 * (self.quant_dtype == torch.bfloat16)
 
     def get_name(self) -> str:
@@ -79,8 +84,9 @@ class MatGPTQConfig(QuantizationConfig):
         path = cls.get_from_keys_or(config, ["bitwidth_config_path"], None)
         if path:
             layer_bitwidths = {**read_bitwidth_config(path), **(layer_bitwidths or {})}
+        zero_points = cls.get_from_keys_or(config, ["zero_points"], False)
         return cls(group_size, master_bitwidth, inference_bitwidth, quant_dtype, modules_to_not_convert,
-                   layer_bitwidths)
+                   layer_bitwidths, zero_points)
 
     def get_quant_method(self, layer: torch.nn.Module, prefix: str) -> QuantizeMethodBase | None:
         if self.modules_to_not_convert is not None and any(
@@ -126,6 +132,11 @@ class MatGPTQLinearMethod(LinearMethodBase):
         set_weight_attrs(scales, {"input_dim": 1, "output_dim": 0, "packed_dim": 1, "pack_factor": 1}
                          | extra_weight_attrs)
         layer.register_parameter("scales", scales)
+        if self.config.zero_points:
+            zeros = Parameter(torch.empty(n_out, groups, dtype=self.config.quant_dtype), requires_grad=False)
+            set_weight_attrs(zeros, {"input_dim": 1, "output_dim": 0, "packed_dim": 1, "pack_factor": 1}
+                             | extra_weight_attrs)
+            layer.register_parameter("zeros", zeros)
 
     def process_weights_after_loading(self, layer: torch.nn.Module) -> None:
         cfg = self.config
@@ -140,10 +151,14 @@ class MatGPTQLinearMethod(LinearMethodBase):
                 segments.append([row, rows, bits])
             row += rows
         with torch.no_grad():
-            packed, scales = [], []
+            packed, scales, zeros = [], [], []
             for row0, rows, bits in segments:
                 q = layer.qweight.data[row0:row0 + rows].contiguous()
                 s = layer.scales.data[row0:row0 + rows].contiguous()
+                if cfg.zero_points:
+                    z = layer.zeros.data[row0:row0 + rows].contiguous()
+                    zeros.append(Parameter(torch.ops.matgptq_cuda.reorder_matgptq_scales(z, rows, n_in, cfg.group_size),
+                                           requires_grad=False))
                 packed.append(Parameter(torch.ops.matgptq_cuda.slice_pack_matgptq_qweights(
                     q, rows, n_in, cfg.master_bitwidth, bits, cfg.group_size, cfg.flag), requires_grad=False))
                 scales.append(Parameter(torch.ops.matgptq_cuda.reorder_matgptq_scales(
@@ -153,14 +168,25 @@ class MatGPTQLinearMethod(LinearMethodBase):
             layer.matgptq_scales = torch.nn.ParameterList(scales)
             del layer.qweight
             del layer.scales
+            if cfg.zero_points:
+                del layer.zeros
+                layer.matgptq_zeros = torch.nn.ParameterList(zeros)
 
     def apply(self, layer: torch.nn.Module, x: torch.Tensor, bias: torch.Tensor | None = None) -> torch.Tensor:
         cfg = self.config
         x2 = x.reshape(-1, x.shape[-1])
-        outs = [
-            torch.ops.matgptq_cuda.matmul_matgptq(x2, w, s, rows, layer.matgptq_n_in, bits, cfg.group_size, cfg.flag)
-            for (rows, bits), w, s in zip(layer.matgptq_segments, layer.matgptq_weights, layer.matgptq_scales)
-        ]
+        if cfg.zero_points:
+            outs = [
+                torch.ops.matgptq_cuda.matmul_matgptq_zeros(x2, w, s, z, rows, layer.matgptq_n_in, bits, cfg.group_size,
+                                                            cfg.flag)
+                for (rows, bits), w, s, z in zip(layer.matgptq_segments, layer.matgptq_weights, layer.matgptq_scales,
+                                                 layer.matgptq_zeros)
+            ]
+        else:
+            outs = [
+                torch.ops.matgptq_cuda.matmul_matgptq(x2, w, s, rows, layer.matgptq_n_in, bits, cfg.group_size, cfg.flag)
+                for (rows, bits), w, s in zip(layer.matgptq_segments, layer.matgptq_weights, layer.matgptq_scales)
+            ]
         y = outs[0] if len(outs) == 1 else torch.cat(outs, dim=-1)
         y = y.view(*x.shape[:-1], y.shape[-1])
         if bias is not None:

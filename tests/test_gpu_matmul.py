@@ -211,3 +211,55 @@ def test_persistent_gemv_llama_shapes(cuda, b, shape, m):
             stream.synchronize()
             assert oracle.rel_err(yg.float().cpu(), ref.float().cpu()) <= 2e-3
     assert _native.device_status() == 0
+
+
+# ---- extension: per-group zero points (asymmetric quantisation) ---------------------------------------------
+
+def _asym_layer_and_ref(n_out, n_in, gs, b, dtype, seed, cuda):
+    layer = synth.make_layer(n_out, n_in, gs, seed=seed, sym=False, dtype=dtype, device=cuda)
+    flag = 1 | (2 if dtype == torch.bfloat16 else 0)
+    packed = torch.ops.matgptq_cuda.slice_pack_matgptq_qweights(layer.qweight, n_out, n_in, 8, b, gs, flag)
+    scales_r = torch.ops.matgptq_cuda.reorder_matgptq_scales(layer.scales, n_out, n_in, gs)
+    zeros_r = torch.ops.matgptq_cuda.reorder_matgptq_scales(layer.zeros, n_out, n_in, gs)
+    w_ref = oracle.dequantize_weight(layer.qweight.cpu(), layer.scales.cpu(), layer.zeros.cpu(), 8, b)
+    return layer, packed, scales_r, zeros_r, w_ref, flag
+
+
+def test_config0_asymmetric_minmax_4096_b4(cuda):
+    """The CPU-runnable case of the benchmark definition: K = N = 4096, one fp16 activation row, weights
+    N(0, 0.02) quantised per group of 128 with asymmetric min-max at 8 bits (fp16 scales and zero points),
+    sliced to 4 bits; output against the dequantise-then-matmul of the oracle on the CPU."""
+    layer, packed, scales_r, zeros_r, w_ref, flag = _asym_layer_and_ref(4096, 4096, 128, 4, torch.float16, 0, cuda)
+    z = layer.zeros.float()
+    assert z.min() < 120 and z.max() > 136  # really asymmetric
+    x = synth.make_activations(1, 4096, seed=0, dtype=torch.float16, device=cuda)
+    y = torch.ops.matgptq_cuda.matmul_matgptq_zeros(x, packed, scales_r, zeros_r, 4096, 4096, 4, 128, flag)
+    y_ref = oracle.linear_fp32_accumulate(x.cpu(), w_ref)
+    assert y.shape == (1, 4096) and y.dtype == torch.float16
+    assert oracle.rel_err(y.cpu(), y_ref) <= TOL
+    # the three-op path on the same codes (implicit zero point 128) must NOT agree: the zero points matter
+    y_sym = torch.ops.matgptq_cuda.matmul_matgptq(x, packed, scales_r, 4096, 4096, 4, 128, flag)
+    assert oracle.rel_err(y_sym.cpu(), y_ref) > 10 * TOL
+
+
+@pytest.mark.parametrize("b", BITS)
+@pytest.mark.parametrize("gs", [-1, 32, 128])
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("m", [1, 5, 16, 37])
+def test_zero_points_ragged(cuda, b, gs, dtype, m):
+    n_out, n_in = 208, 1152
+    layer, packed, scales_r, zeros_r, w_ref, flag = _asym_layer_and_ref(n_out, n_in, gs, b, dtype, 7, cuda)
+    x = synth.make_activations(m, n_in, seed=m, dtype=dtype, device=cuda)
+    y = torch.ops.matgptq_cuda.matmul_matgptq_zeros(x, packed, scales_r, zeros_r, n_out, n_in, b, gs, flag)
+    y_ref = oracle.linear_fp32_accumulate(x.cpu(), w_ref)
+    assert oracle.rel_err(y.cpu(), y_ref) <= TOL
+
+
+def test_zero_points_equal_to_128_match_the_three_op_path(cuda):
+    n_out, n_in, b, m = 1024, 4096, 3, 4
+    packed, scales_r, w_ref, flag = _layer_and_ref(n_out, n_in, 128, b, torch.float16, 5, cuda)
+    zeros_r = torch.full_like(scales_r, 128.0)
+    x = synth.make_activations(m, n_in, seed=3, dtype=torch.float16, device=cuda)
+    y = torch.ops.matgptq_cuda.matmul_matgptq(x, packed, scales_r, n_out, n_in, b, 128, flag)
+    yz = torch.ops.matgptq_cuda.matmul_matgptq_zeros(x, packed, scales_r, zeros_r, n_out, n_in, b, 128, flag)
+    assert torch.equal(y, yz)

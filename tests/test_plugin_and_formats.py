@@ -145,3 +145,40 @@ def test_vllm_method_load_and_apply(plugin, single_rank_tp, cuda, dtype, qd, m):
         rows += p
     y_ref = oracle.linear_fp32_accumulate(x.cpu()[0], torch.cat(w_parts)) + bias.cpu().float()
     assert oracle.rel_err(y.cpu()[0], y_ref) <= 1e-2
+
+
+def test_checkpoint_with_zero_points(tmp_path):
+    shapes = {"model.layers.0.mlp.down_proj": (256, 512)}
+    out = str(tmp_path / "asym")
+    qcfg = ck.write_synthetic_checkpoint(out, shapes, inference_bitwidth=4, sym=False)
+    assert qcfg["zero_points"] is True and ck.read_checkpoint_config(out)["zero_points"] is True
+    q, s, z = ck.load_linear(out, "model.layers.0.mlp.down_proj", with_zeros=True)
+    assert z is not None and z.shape == s.shape and z.dtype == s.dtype and z.float().min() < 120 < 136 < z.float().max()
+    out_sym = str(tmp_path / "sym")
+    assert "zero_points" not in ck.write_synthetic_checkpoint(out_sym, shapes, inference_bitwidth=4)
+    assert ck.load_linear(out_sym, "model.layers.0.mlp.down_proj", with_zeros=True)[2] is None
+
+
+@pytest.mark.gpu
+def test_vllm_method_with_zero_points(plugin, single_rank_tp, cuda):
+    from matgptq_b200 import synth
+    cfg = plugin.MatGPTQConfig.from_config({"group_size": 128, "master_bitwidth": 8, "inference_bitwidth": 4,
+                                            "quant_dtype": "float16", "modules_to_not_convert": ["lm_head", "norm"],
+                                            "zero_points": True})
+    assert cfg.zero_points
+    method = plugin.MatGPTQLinearMethod(cfg, "model.layers.0.mlp.down_proj")
+    n_out, n_in, m = 256, 512, 3
+    layer = _FakeLinear()
+    method.create_weights(layer, n_in, [n_out], n_in, n_out, torch.float16, weight_loader=lambda *a, **k: None)
+    assert tuple(layer.zeros.shape) == (n_out, 4)
+    src = synth.make_layer(n_out, n_in, 128, seed=8, sym=False, dtype=torch.float16)
+    layer.qweight.data.copy_(src.qweight)
+    layer.scales.data.copy_(src.scales)
+    layer.zeros.data.copy_(src.zeros)
+    layer.to(cuda)
+    method.process_weights_after_loading(layer)
+    assert not hasattr(layer, "zeros") and len(layer.matgptq_zeros) == 1
+    x = synth.make_activations(m, n_in, seed=1, dtype=torch.float16, device=cuda)
+    y = method.apply(layer, x)
+    w = oracle.dequantize_weight(src.qweight, src.scales, src.zeros, 8, 4)
+    assert oracle.rel_err(y.cpu(), oracle.linear_fp32_accumulate(x.cpu(), w)) <= 1e-2
