@@ -166,6 +166,58 @@ __device__ __forceinline__ uint32_t dequant_pair(uint32_t v, uint16_t scale, boo
   }
 }
 
+// Dense-weight tiles of the tensor-core path: pair P of a lane as s * (code - Z) * 2^(8-b), bit-exact with
+// dequant_pair(decode_pair(..)) for finite scales, in three instructions for fp16 (LOP3, HFMA2, HMUL2).  The
+// HFMA2 turns 1024 + code*2^p straight into the exact integer (code - Z) * kDensePre; the rest of 2^(8-b)
+// (a factor 2, for b = 2 only, where (1024 + Z) * 64 would leave the fp16 range) is folded into the scale by
+// dense_scale().  The product is rounded once, as in dequantize() (src/quant_utils_matgpqt.py:19-22).
+template <int B> struct DensePre {
+  static constexpr int value = (B == 2) ? 32 : (1 << (8 - B));
+};
+
+template <int B, bool BF16> __device__ __forceinline__ uint32_t dense_scale(uint16_t scale) {
+  constexpr float rest = static_cast<float>((1 << (8 - B)) / DensePre<B>::value);
+  if constexpr (rest == 1.f) return splat16(scale);
+  if constexpr (BF16) {
+    const __nv_bfloat16 v = __hmul(__ushort_as_bfloat16(scale), __float2bfloat16_rn(rest));
+    return splat16(__bfloat16_as_ushort(v));
+  } else {
+    const __half v = __hmul(__ushort_as_half(scale), __float2half_rn(rest));
+    return splat16(__half_as_ushort(v));
+  }
+}
+
+template <int B, int P_OFF> __device__ __forceinline__ uint32_t dense_int_at(uint32_t x) {
+  constexpr int Z = BlockTraits<B>::ZERO;
+  constexpr float pre = static_cast<float>(DensePre<B>::value);
+  constexpr float inv = pre / static_cast<float>(1 << P_OFF);
+  constexpr uint32_t mul = half2_const(inv);
+  constexpr uint32_t add = half2_const(-(1024.0f * inv + static_cast<float>(Z) * pre));
+  return h2_bits(__hfma2(bits_h2(x), bits_h2(mul), bits_h2(add)));
+}
+
+// scale2: dense_scale() of the row's scale
+template <int B, bool BF16>
+__device__ __forceinline__ uint32_t dense_pair(const uint32_t (&w)[2 * B], int P, uint32_t scale2) {
+  const uint32_t x = field_pair<B>(w, P, kMagic);
+  uint32_t v;
+  switch (kstep_offset<B>(P >> 2)) {  // a compile-time constant once the caller's loops are unrolled
+    case 0: v = dense_int_at<B, 0>(x); break;
+    case 2: v = dense_int_at<B, 2>(x); break;
+    case 3: v = dense_int_at<B, 3>(x); break;
+    case 4: v = dense_int_at<B, 4>(x); break;
+    case 6: v = dense_int_at<B, 6>(x); break;
+    default: v = dense_int_at<B, 8>(x); break;
+  }
+  if constexpr (BF16) {
+    const uint32_t vb = h2_to_bf2(v);
+    const __nv_bfloat162 r = __hmul2(*reinterpret_cast<const __nv_bfloat162 *>(&scale2), *reinterpret_cast<const __nv_bfloat162 *>(&vb));
+    return *reinterpret_cast<const uint32_t *>(&r);
+  } else {
+    return h2_bits(__hmul2(bits_h2(scale2), bits_h2(v)));
+  }
+}
+
 // Coalesced load of a lane's words of one block (all lanes of a warp call it).
 __device__ __forceinline__ uint4 ldg_stream_v4(const void *p) {
   uint4 r;

@@ -124,23 +124,10 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&v)[16]) {
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
-// scales of one block for a lane's rows g and g+8 (NG groups per block)
+// scale groups per 128-wide block
 template <int GS> struct TcScales {
   static constexpr int NG = (GS == 32) ? 4 : 1;
-  uint16_t lo[NG], hi[NG];
 };
-
-template <int GS>
-__device__ __forceinline__ void tc_load_scales(const uint16_t *s, int tile16, int kb, int groups, int g, TcScales<GS> &r) {
-  constexpr int NG = TcScales<GS>::NG;
-  const int grp0 = (GS == -1) ? 0 : kb * NG;
-  const uint16_t *base = s + (static_cast<size_t>(tile16) * groups + grp0) * 16 + g;
-#pragma unroll
-  for (int j = 0; j < NG; ++j) {
-    r.lo[j] = __ldg(base + j * 16);
-    r.hi[j] = __ldg(base + j * 16 + 8);
-  }
-}
 
 template <int B, int GS, bool BF16>
 __global__ void __launch_bounds__(kTcThreads, 2) gemm_tc_kernel(const GemmParams p) {
@@ -161,8 +148,8 @@ __global__ void __launch_bounds__(kTcThreads, 2) gemm_tc_kernel(const GemmParams
   const int tile128 = blockIdx.x, sk = blockIdx.y;
   const int m0 = blockIdx.z * 256;
   const int mrows = min(p.M - m0, 256);
-  const int kb_lo = static_cast<int>(static_cast<long long>(sk) * p.kblocks / p.split);
-  const int kb_hi = static_cast<int>(static_cast<long long>(sk + 1) * p.kblocks / p.split);
+  const int kb_lo = sk * p.kblocks / p.split;
+  const int kb_hi = (sk + 1) * p.kblocks / p.split;
   const int nblk = kb_hi - kb_lo;
   const int nit = 2 * nblk;  // pipeline iterations of 64 in-features
   const int groups = (GS == -1) ? 1 : p.K / GS;
@@ -197,55 +184,82 @@ __global__ void __launch_bounds__(kTcThreads, 2) gemm_tc_kernel(const GemmParams
     const int tile16 = tile128 * 8 + warp;
     const bool valid = tile16 < p.N / 16;
     constexpr int BW = BlockTraits<B>::WORDS;
-    const uint32_t *wsrc = p.w + (static_cast<size_t>(valid ? tile16 : 0) * p.kblocks + kb_lo) * BW;
-    // Packed words and scales of three blocks in flight, in statically indexed registers: the block
-    // loop is unrolled by three so that no register is copied while its load is still outstanding.
+    constexpr int NG = TcScales<GS>::NG;
+    // Packed words and scales of two or three blocks in flight, in statically indexed registers: the block
+    // loop is unrolled so that no register is copied while its load is still outstanding.  Everything
+    // inside the loop is a per-lane base plus a running offset: no multiplications, divisions or
+    // modulo by the (runtime) number of stages.
     constexpr int kAhead = (B >= 6) ? 2 : 3;
+    const uint32_t *wnext = p.w + (static_cast<size_t>(valid ? tile16 : 0) * p.kblocks + kb_lo) * BW;  // next block to load
+    const uint16_t *snext = p.s + (static_cast<size_t>(valid ? tile16 : 0) * groups + ((GS == -1) ? 0 : kb_lo * NG)) * 16 + g;
     uint32_t wq[kAhead][2 * B];
-    TcScales<GS> scq[kAhead];
+    uint32_t sq_lo[kAhead][NG], sq_hi[kAhead][NG];  // dense_scale() of the scales of rows g and g+8
+    auto load_next = [&](uint32_t (&wdst)[2 * B], uint32_t (&lo)[NG], uint32_t (&hi)[NG]) {
+      load_block<B>(wnext, lane, wdst);
 #pragma unroll
-    for (int a = 0; a < kAhead; ++a) {
-      if (valid && a < nblk) {
-        load_block<B>(wsrc + static_cast<size_t>(a) * BW, lane, wq[a]);
-        tc_load_scales<GS>(p.s, tile16, kb_lo + a, groups, g, scq[a]);
+      for (int j = 0; j < NG; ++j) {
+        lo[j] = dense_scale<B, BF16>(__ldg(snext + j * 16));
+        hi[j] = dense_scale<B, BF16>(__ldg(snext + j * 16 + 8));
       }
-    }
+      wnext += BW;
+      if (GS != -1) snext += NG * 16;
+    };
+#pragma unroll
+    for (int a = 0; a < kAhead; ++a)
+      if (valid && a < nblk) load_next(wq[a], sq_lo[a], sq_hi[a]);
+
     // Activation tile of iteration j: rows m0.., 64 in-features; row r, 16-byte chunk c goes to
     // r*128 + ((c ^ (r & 7)) << 4) (128-byte swizzle).  It is requested kXAhead iterations early,
-    // one cp.async group per iteration, after the stage it lands in has been released.
+    // one cp.async group per iteration, after the stage it lands in has been released.  A thread copies
+    // chunk c = tid & 7 of the rows tid/8, tid/8 + 32, ...: r & 7 does not change, so its swizzled offset
+    // inside a row is a constant.
     constexpr int kXAhead = 2;
-    auto request_x = [&](int j) -> bool {
-      if (j < nit) {
-        const int sj = j % stages;
-        if (!mbar_wait(bar_empty + sj * 8, ((j / stages) & 1) ^ 1)) return false;
-        const uint32_t stage_b = base_u32 + plan.off_stages + sj * plan.stage_bytes;
-        const uint16_t *xsrc = p.x + static_cast<size_t>(m0) * p.K + static_cast<size_t>(kb_lo + (j >> 1)) * 128 + (j & 1) * 64;
-        for (int idx = tid; idx < mrows * 8; idx += 256) {
-          const int r = idx >> 3, c = idx & 7;
-          cp_async16(stage_b + r * 128 + ((c ^ (r & 7)) << 4), xsrc + static_cast<size_t>(r) * p.K + c * 8);
+    const int xr0 = tid >> 3, xc = tid & 7;
+    const uint32_t xdst_lane = base_u32 + plan.off_stages + xr0 * 128 + ((xc ^ (xr0 & 7)) << 4);
+    const uint16_t *xsrc_lane = p.x + (static_cast<size_t>(m0) + xr0) * p.K + static_cast<size_t>(kb_lo) * 128 + xc * 8;
+    const size_t xrow_step = static_cast<size_t>(32) * p.K;  // halves between two rows of a thread
+    const int xcopies = (mrows - xr0 + 31) >> 5;             // rows this thread copies per iteration
+    int rq_left = nit;                                       // iterations not requested yet
+    uint32_t rq_stage_off = 0, rq_bar = bar_empty, rq_parity = 1;
+    const uint32_t ring_bytes = static_cast<uint32_t>(stages) * plan.stage_bytes;
+    auto request_x = [&]() -> bool {
+      if (rq_left > 0) {
+        if (!mbar_wait(rq_bar, rq_parity)) return false;
+        const uint16_t *src = xsrc_lane;
+        uint32_t dst = xdst_lane + rq_stage_off;
+        for (int i = 0; i < xcopies; ++i) {
+          cp_async16(dst, src);
+          dst += 32 * 128;
+          src += xrow_step;
+        }
+        xsrc_lane += 64;
+        --rq_left;
+        rq_stage_off += plan.stage_bytes;
+        rq_bar += 8;
+        if (rq_stage_off == ring_bytes) {
+          rq_stage_off = 0;
+          rq_bar = bar_empty;
+          rq_parity ^= 1;
         }
       }
       asm volatile("cp.async.commit_group;" ::: "memory");
       return true;
     };
-    for (int j = 0; j < kXAhead; ++j) {
-      if (!request_x(j)) {
-        failed = true;
-        report_status(kStatusMmaTimeout);
-      }
-    }
-    for (int kb0 = 0; kb0 < nblk && !failed; kb0 += kAhead) {
+    for (int j = 0; j < kXAhead; ++j)
+      if (!request_x()) failed = true;
+
+    // this lane's 16 bytes of rows g and g+8 in the A tile of stage 0, chunk t
+    unsigned char *a_lane = base + plan.off_stages + plan.b_stage_bytes + t * kTcChunkStride + (2 * warp) * 128 + g * 16;
+    uint32_t cur_stage_off = 0, cur_bar = bar_full;
+    int blocks_left = nblk, loads_left = nblk - kAhead;
+    while (blocks_left > 0 && !failed) {
 #pragma unroll
       for (int a = 0; a < kAhead; ++a) {
-        const int kbl = kb0 + a;
-        if (kbl < nblk && !failed) {
+        if (blocks_left > 0 && !failed) {
 #pragma unroll
           for (int h = 0; h < 2; ++h) {
-            const int it = 2 * kbl + h;
-            const int s = it % stages;  // released: request_x(it) waited for it
-            if (!request_x(it + kXAhead)) {
+            if (!request_x()) {  // the stage of this iteration was released before its own request was made
               failed = true;
-              report_status(kStatusMmaTimeout);
               break;
             }
             if (valid) {
@@ -254,46 +268,51 @@ __global__ void __launch_bounds__(kTcThreads, 2) gemm_tc_kernel(const GemmParams
               for (int jj = 2 * h; jj < 2 * h + 2; ++jj) {
                 const int gi = (GS == 32) ? jj : 0;
                 uint4 lo, hi;
-                lo.x = dequant_pair<B, BF16>(decode_pair<B>(wq[a], 8 * jj + 0), scq[a].lo[gi], false, 0);
-                lo.y = dequant_pair<B, BF16>(decode_pair<B>(wq[a], 8 * jj + 2), scq[a].lo[gi], false, 0);
-                lo.z = dequant_pair<B, BF16>(decode_pair<B>(wq[a], 8 * jj + 4), scq[a].lo[gi], false, 0);
-                lo.w = dequant_pair<B, BF16>(decode_pair<B>(wq[a], 8 * jj + 6), scq[a].lo[gi], false, 0);
-                hi.x = dequant_pair<B, BF16>(decode_pair<B>(wq[a], 8 * jj + 1), scq[a].hi[gi], false, 0);
-                hi.y = dequant_pair<B, BF16>(decode_pair<B>(wq[a], 8 * jj + 3), scq[a].hi[gi], false, 0);
-                hi.z = dequant_pair<B, BF16>(decode_pair<B>(wq[a], 8 * jj + 5), scq[a].hi[gi], false, 0);
-                hi.w = dequant_pair<B, BF16>(decode_pair<B>(wq[a], 8 * jj + 7), scq[a].hi[gi], false, 0);
-                const int chunk = 4 * (jj & 1) + t;
-                unsigned char *dst = base + plan.off_stages + s * plan.stage_bytes + plan.b_stage_bytes +
-                                     chunk * kTcChunkStride + (2 * warp) * 128 + g * 16;
+                lo.x = dense_pair<B, BF16>(wq[a], 8 * jj + 0, sq_lo[a][gi]);
+                lo.y = dense_pair<B, BF16>(wq[a], 8 * jj + 2, sq_lo[a][gi]);
+                lo.z = dense_pair<B, BF16>(wq[a], 8 * jj + 4, sq_lo[a][gi]);
+                lo.w = dense_pair<B, BF16>(wq[a], 8 * jj + 6, sq_lo[a][gi]);
+                hi.x = dense_pair<B, BF16>(wq[a], 8 * jj + 1, sq_hi[a][gi]);
+                hi.y = dense_pair<B, BF16>(wq[a], 8 * jj + 3, sq_hi[a][gi]);
+                hi.z = dense_pair<B, BF16>(wq[a], 8 * jj + 5, sq_hi[a][gi]);
+                hi.w = dense_pair<B, BF16>(wq[a], 8 * jj + 7, sq_hi[a][gi]);
+                unsigned char *dst = a_lane + cur_stage_off + (jj & 1) * (4 * kTcChunkStride);
                 *reinterpret_cast<uint4 *>(dst) = lo;
                 *reinterpret_cast<uint4 *>(dst + 128) = hi;
               }
             }
-            asm volatile("cp.async.wait_group 2;" ::: "memory");  // = kXAhead: the tile of `it` has landed
+            asm volatile("cp.async.wait_group 2;" ::: "memory");  // = kXAhead: the tile of this iteration has landed
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             __syncwarp();
-            if (lane == 0) mbar_arrive(bar_full + s * 8);
+            if (lane == 0) mbar_arrive(cur_bar);
+            cur_stage_off += plan.stage_bytes;
+            cur_bar += 8;
+            if (cur_stage_off == ring_bytes) {
+              cur_stage_off = 0;
+              cur_bar = bar_full;
+            }
           }
-          // this block's registers are free: fetch the block three ahead
-          if (valid && kbl + kAhead < nblk) {
-            load_block<B>(wsrc + static_cast<size_t>(kbl + kAhead) * BW, lane, wq[a]);
-            tc_load_scales<GS>(p.s, tile16, kb_lo + kbl + kAhead, groups, g, scq[a]);
-          }
+          // this block's registers are free: fetch the block kAhead ahead
+          if (valid && loads_left > 0) load_next(wq[a], sq_lo[a], sq_hi[a]);
+          --loads_left;
+          --blocks_left;
         }
       }
     }
+    if (failed) report_status(kStatusMmaTimeout);
   } else if (warp == 8 && lane == 0) {
     // ------------------------------------------------------------------ MMA issuer
     const uint32_t idesc = umma_instr_desc(BF16 ? 1 : 0, p.ncols);
+    uint32_t st_off = 0, st_idx8 = 0, parity = 0;
+    const uint32_t ring_bytes = static_cast<uint32_t>(stages) * plan.stage_bytes;
     for (int it = 0; it < nit && !failed; ++it) {
-      const int s = it % stages;
-      if (!mbar_wait(bar_full + s * 8, (it / stages) & 1)) {
+      if (!mbar_wait(bar_full + st_idx8, parity)) {
         failed = true;
         report_status(kStatusWeightCopyTimeout);
         break;
       }
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      const uint32_t stage_b = base_u32 + plan.off_stages + s * plan.stage_bytes;
+      const uint32_t stage_b = base_u32 + plan.off_stages + st_off;
       const uint32_t stage_a = stage_b + plan.b_stage_bytes;
 #pragma unroll
       for (int k = 0; k < 4; ++k) {
@@ -301,7 +320,14 @@ __global__ void __launch_bounds__(kTcThreads, 2) gemm_tc_kernel(const GemmParams
         const uint64_t db = umma_smem_desc(stage_b + k * 32, 16, 1024, 2);
         umma_f16(tmem_base, da, db, idesc, (it > 0 || k > 0) ? 1u : 0u);
       }
-      umma_commit(bar_empty + s * 8);
+      umma_commit(bar_empty + st_idx8);
+      st_off += plan.stage_bytes;
+      st_idx8 += 8;
+      if (st_off == ring_bytes) {
+        st_off = 0;
+        st_idx8 = 0;
+        parity ^= 1;
+      }
     }
     if (!failed) umma_commit(bar_done);
   }
