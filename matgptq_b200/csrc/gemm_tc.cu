@@ -409,10 +409,15 @@ template <int B, int GS, bool BF16>
 static int launch_gemm_tc(GemmParams p, cudaStream_t stream, bool pdl) {
   auto kernel = gemm_tc_kernel<B, GS, BF16>;
   p.ncols = round_up16(p.M < 256 ? p.M : 256);
-  // four stages, or three where that lets a second CTA share the SM
-  int stages = 4;
-  if (tc_plan(p.ncols, 4).total > 110 * 1024 && tc_plan(p.ncols, 3).total <= 110 * 1024) stages = 3;
-  while (stages > 3 && tc_plan(p.ncols, stages).total > 200 * 1024) --stages;
+  // The producers may run (stages - 2) iterations ahead of the tensor pipe, and every iteration costs a round
+  // trip through two mbarriers, so depth matters more than anything else here: as many stages as fit in half
+  // of an SM's shared memory when that is at least four (two CTAs per SM), else as many as one CTA can have.
+  int stages = 8;
+  while (stages > 4 && tc_plan(p.ncols, stages).total > 112 * 1024) --stages;
+  if (tc_plan(p.ncols, stages).total > 112 * 1024) {
+    stages = 8;
+    while (stages > 2 && tc_plan(p.ncols, stages).total > 224 * 1024) --stages;
+  }
   p.stages = stages;
   const TcPlan plan = tc_plan(p.ncols, stages);
   static bool opted_in[64] = {};
@@ -420,7 +425,7 @@ static int launch_gemm_tc(GemmParams p, cudaStream_t stream, bool pdl) {
   if (cudaGetDevice(&dev) != cudaSuccess) return MG_ERR_CUDA;
   if (dev < 0 || dev >= 64) return MG_ERR_BAD_ARG;
   if (!opted_in[dev]) {
-    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) != cudaSuccess) return MG_ERR_CUDA;
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 224 * 1024) != cudaSuccess) return MG_ERR_CUDA;
     opted_in[dev] = true;
   }
   cudaLaunchConfig_t cfg = {};
