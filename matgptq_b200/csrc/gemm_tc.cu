@@ -9,18 +9,19 @@
 //     block to the exact dense weights of the reference's dequantize()
 //     (round(scale * (code*2^(8-b) - 128)), fp16 or bf16) and store them K-major into a
 //     shared-memory stage in the canonical no-swizzle UMMA layout (8 x 16-byte core
-//     matrices), with the packed words of the next three blocks already in flight; the
-//     same warps copy the activation tile into the 128-byte-swizzled K-major layout with
-//     cp.async, two pipeline stages ahead of the weights they are decoding;
-//   * a ninth warp issues tcgen05.mma (M = 128 weights rows, N = batch rows, K = 16)
-//     from shared-memory descriptors; D[128, N] lives in tensor memory; completion
-//     of a stage's MMAs releases the stage through tcgen05.commit -> mbarrier;
+//     matrices), with the packed words of the next two or three blocks already in flight;
+//   * one thread of a ninth warp fetches the activation tiles (batch rows x 64 in-features) with TMA
+//     (cp.async.bulk.tensor.2d, 128-byte swizzle, rows past the batch filled with zeros), as far ahead as
+//     the pipeline has stages, and issues tcgen05.mma (M = 128 weight rows, N = batch rows, K = 16)
+//     from shared-memory descriptors; D[128, N] lives in tensor memory; completion of a stage's MMAs
+//     releases the stage through tcgen05.commit -> mbarrier;
 //   * the epilogue reads D with tcgen05.ld (each warp its own 32 TMEM lanes), converts
 //     and stores y[m, n] (the transpose of D), or, when K is split over several CTAs,
 //     stores fp32 partial sums into caller-provided scratch memory that a second small
 //     kernel adds up in a fixed order.
 //
 // Every mbarrier wait is bounded (async.cuh); tensor memory is freed on every path.
+#include <cuda.h>  // CUtensorMap and its enums; cuTensorMapEncodeTiled is resolved at run time
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
@@ -54,8 +55,12 @@ __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
 
-__device__ __forceinline__ void cp_async16(uint32_t dst, const void *src) {
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+// TMA load of one box of a 2-D tensor map into shared memory; x (the innermost coordinate) times the element
+// size must be a multiple of 16 bytes: here x is a multiple of 64 two-byte elements.
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, int x, int y, uint32_t bar) {
+  asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(dst),
+               "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(bar)
+               : "memory");
 }
 
 // 64-bit shared-memory matrix descriptor (K-major).  layout_type: 0 = no swizzle, 2 = 128-byte swizzle.
@@ -130,7 +135,7 @@ template <int GS> struct TcScales {
 };
 
 template <int B, int GS, bool BF16>
-__global__ void __launch_bounds__(kTcThreads, 2) gemm_tc_kernel(const GemmParams p) {
+__global__ void __launch_bounds__(kTcThreads, 2) gemm_tc_kernel(const GemmParams p, const __grid_constant__ CUtensorMap xmap) {
   extern __shared__ unsigned char tc_smem_raw[];
   const uint32_t raw_u32 = smem_u32(tc_smem_raw);
   const uint32_t base_u32 = (raw_u32 + 1023u) & ~1023u;
@@ -140,7 +145,7 @@ __global__ void __launch_bounds__(kTcThreads, 2) gemm_tc_kernel(const GemmParams
   const int g = lane >> 2, t = lane & 3;
   const int stages = p.stages;
   const TcPlan plan = tc_plan(p.ncols, stages);
-  const uint32_t bar_full = base_u32;               // stages barriers, 8 arrivals each
+  const uint32_t bar_full = base_u32;               // stages barriers: 8 producer warps + the TMA issuer (and its bytes)
   const uint32_t bar_empty = base_u32 + 8 * 8;      // stages barriers, released by tcgen05.commit
   const uint32_t bar_done = base_u32 + 16 * 8;
   volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(base + 17 * 8);
@@ -159,7 +164,7 @@ __global__ void __launch_bounds__(kTcThreads, 2) gemm_tc_kernel(const GemmParams
   if (warp == 8) {
     if (lane == 0) {
       for (int i = 0; i < stages; ++i) {
-        mbar_init(bar_full + i * 8, 8);  // the eight producer warps
+        mbar_init(bar_full + i * 8, 9);  // the eight producer warps and the thread that requests the activations
         mbar_init(bar_empty + i * 8, 1);
       }
       mbar_init(bar_done, 1);
@@ -208,49 +213,10 @@ __global__ void __launch_bounds__(kTcThreads, 2) gemm_tc_kernel(const GemmParams
     for (int a = 0; a < kAhead; ++a)
       if (valid && a < nblk) load_next(wq[a], sq_lo[a], sq_hi[a]);
 
-    // Activation tile of iteration j: rows m0.., 64 in-features; row r, 16-byte chunk c goes to
-    // r*128 + ((c ^ (r & 7)) << 4) (128-byte swizzle).  It is requested kXAhead iterations early,
-    // one cp.async group per iteration, after the stage it lands in has been released.  A thread copies
-    // chunk c = tid & 7 of the rows tid/8, tid/8 + 32, ...: r & 7 does not change, so its swizzled offset
-    // inside a row is a constant.
-    constexpr int kXAhead = 2;
-    const int xr0 = tid >> 3, xc = tid & 7;
-    const uint32_t xdst_lane = base_u32 + plan.off_stages + xr0 * 128 + ((xc ^ (xr0 & 7)) << 4);
-    const uint16_t *xsrc_lane = p.x + (static_cast<size_t>(m0) + xr0) * p.K + static_cast<size_t>(kb_lo) * 128 + xc * 8;
-    const size_t xrow_step = static_cast<size_t>(32) * p.K;  // halves between two rows of a thread
-    const int xcopies = (mrows - xr0 + 31) >> 5;             // rows this thread copies per iteration
-    int rq_left = nit;                                       // iterations not requested yet
-    uint32_t rq_stage_off = 0, rq_bar = bar_empty, rq_parity = 1;
     const uint32_t ring_bytes = static_cast<uint32_t>(stages) * plan.stage_bytes;
-    auto request_x = [&]() -> bool {
-      if (rq_left > 0) {
-        if (!mbar_wait(rq_bar, rq_parity)) return false;
-        const uint16_t *src = xsrc_lane;
-        uint32_t dst = xdst_lane + rq_stage_off;
-        for (int i = 0; i < xcopies; ++i) {
-          cp_async16(dst, src);
-          dst += 32 * 128;
-          src += xrow_step;
-        }
-        xsrc_lane += 64;
-        --rq_left;
-        rq_stage_off += plan.stage_bytes;
-        rq_bar += 8;
-        if (rq_stage_off == ring_bytes) {
-          rq_stage_off = 0;
-          rq_bar = bar_empty;
-          rq_parity ^= 1;
-        }
-      }
-      asm volatile("cp.async.commit_group;" ::: "memory");
-      return true;
-    };
-    for (int j = 0; j < kXAhead; ++j)
-      if (!request_x()) failed = true;
-
     // this lane's 16 bytes of rows g and g+8 in the A tile of stage 0, chunk t
     unsigned char *a_lane = base + plan.off_stages + plan.b_stage_bytes + t * kTcChunkStride + (2 * warp) * 128 + g * 16;
-    uint32_t cur_stage_off = 0, cur_bar = bar_full;
+    uint32_t cur_stage_off = 0, cur_bar = bar_full, cur_empty = bar_empty, cur_parity = 1;
     int blocks_left = nblk, loads_left = nblk - kAhead;
     while (blocks_left > 0 && !failed) {
 #pragma unroll
@@ -258,7 +224,7 @@ __global__ void __launch_bounds__(kTcThreads, 2) gemm_tc_kernel(const GemmParams
         if (blocks_left > 0 && !failed) {
 #pragma unroll
           for (int h = 0; h < 2; ++h) {
-            if (!request_x()) {  // the stage of this iteration was released before its own request was made
+            if (!mbar_wait(cur_empty, cur_parity)) {  // the tensor pipe is done with what this stage held
               failed = true;
               break;
             }
@@ -281,15 +247,17 @@ __global__ void __launch_bounds__(kTcThreads, 2) gemm_tc_kernel(const GemmParams
                 *reinterpret_cast<uint4 *>(dst + 128) = hi;
               }
             }
-            asm volatile("cp.async.wait_group 2;" ::: "memory");  // = kXAhead: the tile of this iteration has landed
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy stores -> tensor pipe reads
             __syncwarp();
             if (lane == 0) mbar_arrive(cur_bar);
             cur_stage_off += plan.stage_bytes;
             cur_bar += 8;
+            cur_empty += 8;
             if (cur_stage_off == ring_bytes) {
               cur_stage_off = 0;
               cur_bar = bar_full;
+              cur_empty = bar_empty;
+              cur_parity ^= 1;
             }
           }
           // this block's registers are free: fetch the block kAhead ahead
@@ -305,7 +273,36 @@ __global__ void __launch_bounds__(kTcThreads, 2) gemm_tc_kernel(const GemmParams
     const uint32_t idesc = umma_instr_desc(BF16 ? 1 : 0, p.ncols);
     uint32_t st_off = 0, st_idx8 = 0, parity = 0;
     const uint32_t ring_bytes = static_cast<uint32_t>(stages) * plan.stage_bytes;
+    // Activation tiles: iteration j needs rows m0.. and in-features (kb_lo*128 + 64 j ..+64) in the B part of its
+    // stage.  They are requested a few iterations ahead, each after the stage has been released.
+    uint32_t rq_off = 0, rq_idx8 = 0, rq_parity = 1;
+    int rq_x = kb_lo * 128, rq_left = nit;
+    auto request_x = [&]() -> bool {
+      if (rq_left <= 0) return true;
+      if (!mbar_wait(bar_empty + rq_idx8, rq_parity)) return false;
+      mbar_arrive_expect_tx(bar_full + rq_idx8, plan.b_stage_bytes);
+      tma_load_2d(base_u32 + plan.off_stages + rq_off, &xmap, rq_x, m0, bar_full + rq_idx8);
+      rq_x += 64;
+      --rq_left;
+      rq_off += plan.stage_bytes;
+      rq_idx8 += 8;
+      if (rq_off == ring_bytes) {
+        rq_off = 0;
+        rq_idx8 = 0;
+        rq_parity ^= 1;
+      }
+      return true;
+    };
+    // two stages short of the ring, so that the wait inside request_x() is for MMAs issued two iterations ago
+    const int ahead = stages > 3 ? stages - 2 : 1;
+    for (int j = 0; j < ahead; ++j)
+      if (!request_x()) failed = true;
     for (int it = 0; it < nit && !failed; ++it) {
+      if (!request_x()) {
+        failed = true;
+        report_status(kStatusMmaTimeout);
+        break;
+      }
       if (!mbar_wait(bar_full + st_idx8, parity)) {
         failed = true;
         report_status(kStatusWeightCopyTimeout);
@@ -405,10 +402,35 @@ long long gemm_tc_workspace_bytes(int N, int K, int M, int sm_count) {
   return split > 1 ? static_cast<long long>(split) * M * N * 4 : 0;
 }
 
+// Tensor map of the activations x[M, K] (two-byte elements, row-major) with boxes of 64 in-features x `box_rows`
+// batch rows and the 128-byte swizzle the UMMA descriptor of the B operand expects; rows past M read as zeros.
+static int make_x_tensor_map(CUtensorMap *map, const void *x, int M, int K, int box_rows) {
+  typedef CUresult (*EncodeTiled)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
+                                  const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+  static EncodeTiled encode = nullptr;
+  if (!encode) {
+    void *fn = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q) != cudaSuccess || !fn) return MG_ERR_CUDA;
+    encode = reinterpret_cast<EncodeTiled>(fn);
+  }
+  const cuuint64_t gdim[2] = {static_cast<cuuint64_t>(K), static_cast<cuuint64_t>(M)};
+  const cuuint64_t gstride[1] = {static_cast<cuuint64_t>(K) * 2};
+  const cuuint32_t box[2] = {64u, static_cast<cuuint32_t>(box_rows)};
+  const cuuint32_t estride[2] = {1u, 1u};
+  const CUresult r = encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, const_cast<void *>(x), gdim, gstride, box, estride,
+                            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? MG_OK : MG_ERR_CUDA;
+}
+
 template <int B, int GS, bool BF16>
 static int launch_gemm_tc(GemmParams p, cudaStream_t stream, bool pdl) {
   auto kernel = gemm_tc_kernel<B, GS, BF16>;
   p.ncols = round_up16(p.M < 256 ? p.M : 256);
+  CUtensorMap xmap;
+  if (make_x_tensor_map(&xmap, p.x, p.M, p.K, p.ncols) != MG_OK) return MG_ERR_CUDA;
   // The producers may run (stages - 2) iterations ahead of the tensor pipe, and every iteration costs a round
   // trip through two mbarriers, so depth matters more than anything else here: as many stages as fit in half
   // of an SM's shared memory when that is at least four (two CTAs per SM), else as many as one CTA can have.
@@ -442,7 +464,7 @@ static int launch_gemm_tc(GemmParams p, cudaStream_t stream, bool pdl) {
   }
   cfg.attrs = attrs;
   cfg.numAttrs = na;
-  if (cudaLaunchKernelEx(&cfg, kernel, p) != cudaSuccess) return MG_ERR_CUDA;
+  if (cudaLaunchKernelEx(&cfg, kernel, p, xmap) != cudaSuccess) return MG_ERR_CUDA;
   if (p.split > 1) {
     const long long mn = static_cast<long long>(p.M) * p.N;
     long long blocks = (mn + 255) / 256;
