@@ -372,6 +372,9 @@ __global__ void __launch_bounds__(kTcThreads, 2) gemm_tc_kernel(const GemmParams
 // partial[split][M][N] fp32 -> y[M][N], added in a fixed order
 template <bool BF16>
 __global__ void splitk_reduce_kernel(const float *__restrict__ partial, uint16_t *__restrict__ y, long long mn, int split) {
+  // launched with programmatic stream serialization right behind the kernel that writes `partial`
+  asm volatile("griddepcontrol.launch_dependents;");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < mn;
        i += static_cast<long long>(gridDim.x) * blockDim.x) {
     float sum = 0.f;
@@ -385,13 +388,19 @@ __global__ void splitk_reduce_kernel(const float *__restrict__ partial, uint16_t
 // ----------------------------------------------------------------------------
 static int round_up16(int v) { return (v + 15) / 16 * 16; }
 
-// K split of the tensor-core path: the decode is latency bound with eight producer warps per CTA,
-// so aim at two CTAs per SM where the pipeline stages of two CTAs fit in shared memory (up to 128
-// batch rows), one otherwise; at least four blocks of K per CTA.
+// Up to 128 batch rows the kernel is bound by its producer warps (eight per CTA), so two CTAs share an SM
+// whenever three pipeline stages of each fit in half of the SM's shared memory.  Measured on B200: two stages
+// are too shallow (256 batch rows: 45 us with one CTA and four stages, 53 us with two CTAs and two stages),
+// and at 256 rows sixteen producer warps in one CTA change nothing (the tensor pipe of the 112 to 128 SMs
+// that have a tile is then the limit).
+constexpr int kTcHalfSmBytes = 112 * 1024;
+static bool tc_two_ctas_per_sm(int ncols) { return tc_plan(ncols, 3).total <= kTcHalfSmBytes; }
+
+// K split of the tensor-core path: one wave of CTAs over the SMs' slots; at least four blocks of K per CTA.
 int gemm_tc_pick_split(int N, int K, int M, int sm_count) {
   const int ctas = ((N + 127) / 128) * ((M + 255) / 256);
   const int kblocks = K / 128;
-  const int want = (M <= 128) ? 2 * sm_count : sm_count;
+  const int want = tc_two_ctas_per_sm(round_up16(M < 256 ? M : 256)) ? 2 * sm_count : sm_count;
   int split = 1;
   while (split < 8 && ctas * (split + 1) <= want && kblocks / (split + 1) >= 4) ++split;  // one wave
   return split;
@@ -431,14 +440,11 @@ static int launch_gemm_tc(GemmParams p, cudaStream_t stream, bool pdl) {
   p.ncols = round_up16(p.M < 256 ? p.M : 256);
   CUtensorMap xmap;
   if (make_x_tensor_map(&xmap, p.x, p.M, p.K, p.ncols) != MG_OK) return MG_ERR_CUDA;
-  // The producers may run (stages - 2) iterations ahead of the tensor pipe, and every iteration costs a round
-  // trip through two mbarriers, so depth matters more than anything else here: as many stages as fit in half
-  // of an SM's shared memory when that is at least four (two CTAs per SM), else as many as one CTA can have.
   int stages = 8;
-  while (stages > 4 && tc_plan(p.ncols, stages).total > 112 * 1024) --stages;
-  if (tc_plan(p.ncols, stages).total > 112 * 1024) {
-    stages = 8;
-    while (stages > 2 && tc_plan(p.ncols, stages).total > 224 * 1024) --stages;
+  if (tc_two_ctas_per_sm(p.ncols)) {
+    while (stages > 3 && tc_plan(p.ncols, stages).total > kTcHalfSmBytes) --stages;
+  } else {
+    while (stages > 2 && tc_plan(p.ncols, stages).total > 2 * kTcHalfSmBytes) --stages;
   }
   p.stages = stages;
   const TcPlan plan = tc_plan(p.ncols, stages);
@@ -469,8 +475,17 @@ static int launch_gemm_tc(GemmParams p, cudaStream_t stream, bool pdl) {
     const long long mn = static_cast<long long>(p.M) * p.N;
     long long blocks = (mn + 255) / 256;
     if (blocks > 148 * 8) blocks = 148 * 8;
-    splitk_reduce_kernel<BF16><<<static_cast<unsigned>(blocks), 256, 0, stream>>>(p.partial, p.y, mn, p.split);
-    if (cudaGetLastError() != cudaSuccess) return MG_ERR_CUDA;
+    cudaLaunchConfig_t rcfg = {};
+    rcfg.gridDim = dim3(static_cast<unsigned>(blocks), 1, 1);
+    rcfg.blockDim = dim3(256, 1, 1);
+    rcfg.stream = stream;
+    cudaLaunchAttribute rattr[1];
+    rattr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    rattr[0].val.programmaticStreamSerializationAllowed = 1;
+    rcfg.attrs = rattr;
+    rcfg.numAttrs = 1;
+    if (cudaLaunchKernelEx(&rcfg, splitk_reduce_kernel<BF16>, static_cast<const float *>(p.partial), p.y, mn, p.split) != cudaSuccess)
+      return MG_ERR_CUDA;
   }
   return MG_OK;
 }
