@@ -38,10 +38,11 @@ def _sources() -> list[str]:
 
 
 def _newest_header_mtime() -> float:
+    """Newest header, or source that another source includes (gemv_zp.cu compiles gemv.cu a second time)."""
     mt = 0.0
     for d in (CSRC, INCLUDE):
         for name in os.listdir(d):
-            if name.endswith((".h", ".cuh")):
+            if name.endswith((".h", ".cuh")) or name == "gemv.cu":
                 mt = max(mt, os.path.getmtime(os.path.join(d, name)))
     return mt
 
