@@ -416,7 +416,7 @@ def ours_main(args) -> None:
 
 
 def run_decode(world: int, rank: int, dev: torch.device, model_name: str, batch: int, prompt_len: int, new_tokens: int,
-               mean_bits: float, layers: int | None = None) -> dict:
+               mean_bits: float, layers: int | None = None, uniform_bits: int = 0) -> dict:
     """Greedy decode of a random-init Llama-architecture model over packed linears: random prompt ids,
     seeded per-layer bitwidths from {2,3,4,6,8} with the given parameter-weighted mean, one CUDA-graph
     replay per token; tok/s = generated tokens * batch / device time of the decode phase (max over ranks)."""
@@ -424,8 +424,11 @@ def run_decode(world: int, rank: int, dev: torch.device, model_name: str, batch:
     shape = {"8b": decode.LLAMA31_8B, "70b": decode.LLAMA31_70B}[model_name]
     if layers:
         shape = decode.LlamaShape(shape.hidden, shape.intermediate, shape.n_heads, shape.n_kv_heads, layers, shape.vocab)
-    bits = decode.mixed_bitwidths(shape, mean_bits, seed=0)
     names = decode.layer_names(shape)
+    if uniform_bits:
+        bits = {n: uniform_bits for n in names}
+    else:
+        bits = decode.mixed_bitwidths(shape, mean_bits, seed=0)
     achieved_bits = sum(bits[n] * names[n] for n in names) / sum(names.values())
     progress(f"decode: building {model_name} batch {batch}")
     model = decode.PackedLlama(shape, bits, dtype=torch.float16, tp_rank=rank, tp_size=world, seed=0, batch=batch,
@@ -574,8 +577,9 @@ def decode_main(args) -> None:
         progress("bringing the process group up")
         torch.distributed.init_process_group("nccl", device_id=dev)
     parts = args.decode.split(":")
-    r = run_decode(world, rank, dev, parts[0], int(parts[1]), int(parts[2]), int(parts[3]), float(parts[4]),
-                   int(parts[5]) if len(parts) > 5 else None)
+    uniform = int(parts[4][1:]) if parts[4].startswith("u") else 0  # "u4": every layer at 4 bits
+    r = run_decode(world, rank, dev, parts[0], int(parts[1]), int(parts[2]), int(parts[3]),
+                   0.0 if uniform else float(parts[4]), int(parts[5]) if len(parts) > 5 else None, uniform_bits=uniform)
     if rank == 0:
         print(json.dumps({"metric": "decode_tokens_per_s", "value": r["tok_per_s"], "unit": "tok/s", "n_gpus": world, **r}), flush=True)
     if world > 1:
@@ -596,7 +600,8 @@ def main() -> None:
     ap.add_argument("--no-table", action="store_true", help="skip the per-cell cold-L2 table")
     ap.add_argument("--no-decode", action="store_true", help="skip the whole-model decode measurement")
     ap.add_argument("--decode", type=str, default=None,
-                    help="model:batch:prompt:new:mean_bits[:layers], e.g. 70b:16:512:256:3.5 - only run this decode and exit")
+                    help="model:batch:prompt:new:bits[:layers] - only run this decode and exit; bits is the mean of a seeded "
+                         "per-layer mixture (70b:16:512:256:3.5) or uN for N bits everywhere (70b:1:512:256:u4)")
     args = ap.parse_args()
     if args.decode:
         decode_main(args)
