@@ -285,22 +285,31 @@ __global__ void __launch_bounds__(512, 1) gemv_kernel(const GemvParams p) {
 #pragma unroll
       for (int nt = 0; nt < NT; ++nt) {
         const uint16_t *xp = x_lane[nt] + (xi & 1) * xbuf_halves + blk * 128;
-        float sacc[4];
+        if constexpr (GS == 32) {
 #pragma unroll
-        for (int jj = 0; jj < 4; ++jj) {
-          const uint4 xv = *reinterpret_cast<const uint4 *>(xp + 32 * jj);
-          if (GS == 32 || jj == 0)
+          for (int jj = 0; jj < 4; ++jj) {
+            const uint4 xv = *reinterpret_cast<const uint4 *>(xp + 32 * jj);
+            float sacc[4];
             mma16816<true>(sacc, ones, xv.x, xv.y);
-          else
-            mma16816<false>(sacc, ones, xv.x, xv.y);
-          mma16816<false>(sacc, ones, xv.z, xv.w);
-          if (GS == 32 && g == 0)
-            *reinterpret_cast<float2 *>(xsum + blk * kSumsPerBlock + jj * (NT * 8) + nt * 8 + 2 * t) =
-                make_float2(kNegZero * sacc[0], kNegZero * sacc[1]);
+            mma16816<false>(sacc, ones, xv.z, xv.w);
+            if (g == 0)
+              *reinterpret_cast<float2 *>(xsum + blk * kSumsPerBlock + jj * (NT * 8) + nt * 8 + 2 * t) =
+                  make_float2(kNegZero * sacc[0], kNegZero * sacc[1]);
+          }
+        } else {
+          // four independent accumulators, added at the end: the chain of dependent MMAs is two deep, not eight
+          float sacc[4][4];
+#pragma unroll
+          for (int jj = 0; jj < 4; ++jj) {
+            const uint4 xv = *reinterpret_cast<const uint4 *>(xp + 32 * jj);
+            mma16816<true>(sacc[jj], ones, xv.x, xv.y);
+            mma16816<false>(sacc[jj], ones, xv.z, xv.w);
+          }
+          if (g == 0)
+            *reinterpret_cast<float2 *>(xsum + blk * kSumsPerBlock + nt * 8 + 2 * t) =
+                make_float2(kNegZero * ((sacc[0][0] + sacc[1][0]) + (sacc[2][0] + sacc[3][0])),
+                            kNegZero * ((sacc[0][1] + sacc[1][1]) + (sacc[2][1] + sacc[3][1])));
         }
-        if (GS != 32 && g == 0)
-          *reinterpret_cast<float2 *>(xsum + blk * kSumsPerBlock + nt * 8 + 2 * t) =
-              make_float2(kNegZero * sacc[0], kNegZero * sacc[1]);
       }
     }
     __syncthreads();
