@@ -87,6 +87,8 @@ class PackedLinear:
 
     def __call__(self, x: torch.Tensor, pdl: bool = False) -> torch.Tensor:
         flag = self.flag | (_native.FLAG_PDL if pdl else 0)
+        # (running the segments on parallel streams was measured: 419 tok/s against 446 at batch 1; the fork
+        # and join events cost more than the overlap gives, and the launches lose their programmatic chaining)
         if x.shape[0] == 1 and len(self.parts) > 1:  # one row: every segment writes its slice of the result in place
             out, col = torch.empty(1, self.n_out, dtype=x.dtype, device=x.device), 0
             for rows, bits, packed, scales in self.parts:
