@@ -14,8 +14,9 @@
 //     (exact integers), multiplies them with the activation fragments on the
 //     tensor pipe into a per-group fp32 accumulator and folds the group's scale in
 //     fp32 (one FMA per accumulator and group);
-//   * the R warps of a CTA cover R consecutive row tiles over the same K slice and
-//     share the activation slice staged once in shared memory;
+//   * the R warps of a CTA are Rt consecutive row tiles x RK slices of the CTA's K range
+//     and share the activations staged in shared memory: the CTA's whole K slice in one
+//     piece when it fits (no barrier inside the loop), else double-buffered stages;
 //   * K is split over the S CTAs of a thread-block cluster (split-K for skinny
 //     shapes); every CTA stores its partial sums into the shared memory of the CTA
 //     that owns the columns (distributed shared memory), which adds them in a fixed
