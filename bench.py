@@ -36,9 +36,11 @@ BATCHES = (1, 2, 4, 8, 16)
 BITS = synth.BITWIDTHS
 GROUP = 128
 ROW_PARALLEL = {"q_o": True, "k_v": False, "gate_up": False, "down": True}
-# dram__bytes_read+write of mg::gemv_kernel divided by its algorithmic bytes, from the ncu capture
-# summarised in profiles/gemv_gate_up_b4_m1_full.md (30.32 MB measured / 30.31 MB algorithmic)
+# dram__bytes_read+write of mg::gemv_kernel divided by its algorithmic bytes, from an ncu capture of
+# gate/up at 4 bits, one activation row (30.32 MB measured / 30.31 MB algorithmic)
 DRAM_TRAFFIC_PER_ALGORITHMIC_BYTE = 1.0002
+# warm-up replays of the sweep graph when it holds collectives (the same on every rank, see ours_main)
+MULTI_RANK_WARMUP_REPLAYS = 192
 
 
 def measured_peaks() -> tuple[float, str]:
@@ -104,9 +106,8 @@ class ClockSampler:
 # reference arm / CPU baseline: the oracle's dequantise-then-matmul on the host cores
 # --------------------------------------------------------------------------------------
 def cpu_sample_cells():
-    """Bounded sample of the sweep for the CPU arm: M = 1, q/o shape, every bitwidth."""
-    k, n = synth.LLAMA3_8B_SHAPES["q_o"]
-    return [("q_o", k, n, 1, b) for b in BITS]
+    """Bounded sample of the sweep for the CPU arm: every shape and every bitwidth at M = 1 (20 of the 100 cells)."""
+    return [(name, k, n, 1, b) for name, (k, n) in synth.LLAMA3_8B_SHAPES.items() for b in BITS]
 
 
 def run_cpu_arm(steps: int, warmup: int) -> dict:
@@ -114,14 +115,16 @@ def run_cpu_arm(steps: int, warmup: int) -> dict:
     cores = os.cpu_count() or 1
     torch.set_num_threads(cores)
     cells = cpu_sample_cells()
-    layer = synth.make_layer(4096, 4096, GROUP, seed=1, sym=True, dtype=torch.float16)
-    x = synth.make_activations(1, 4096, seed=1, dtype=torch.float16)
+    layers = {name: synth.make_layer(n, k, GROUP, seed=1 + i, sym=True, dtype=torch.float16)
+              for i, (name, (k, n)) in enumerate(synth.LLAMA3_8B_SHAPES.items())}
+    xs = {k: synth.make_activations(1, k, seed=1, dtype=torch.float16) for k in {k for _, k, _, _, _ in cells}}
     nbytes = sum(synth.algorithmic_bytes(n, k, m, b, GROUP) for _, k, n, m, b in cells)
 
     parts = [0.0, 0.0]  # seconds in dequantize() and in F.linear, over the timed steps
 
     def step(timed: bool = False):
-        for _, k, n, m, b in cells:
+        for name, k, n, m, b in cells:
+            layer, x = layers[name], xs[k]
             # the two halves of oracle.fake_matryoshka_linear (FakeMatryoshkaLinear.forward), timed apart
             t0 = time.perf_counter()
             w = oracle.dequantize_weight(layer.qweight, layer.scales, layer.zeros, 8, b)
@@ -140,7 +143,8 @@ def run_cpu_arm(steps: int, warmup: int) -> dict:
     dt = (time.perf_counter() - t0) / steps
     return {"value": nbytes / dt / 1e9, "ms_per_step": dt * 1e3, "cores": cores,
             "dequant_ms_per_step": parts[0] / steps * 1e3, "matmul_ms_per_step": parts[1] / steps * 1e3,
-            "sample": "oracle dequantise-then-matmul (torch CPU, fp16), 4096x4096, M=1, b in {2,3,4,6,8}: 5 cells per step"}
+            "sample": "oracle dequantise-then-matmul (torch CPU, fp16), the four Llama-3-8B shapes x b in {2,3,4,6,8} "
+                      "at M=1: 20 of the sweep's 100 cells per step"}
 
 
 def reference_main(args) -> None:
@@ -165,18 +169,30 @@ def reference_main(args) -> None:
 # --------------------------------------------------------------------------------------
 # our arm
 # --------------------------------------------------------------------------------------
+def shard_shape(name: str, world: int) -> tuple[int, int]:
+    """(k_loc, n_loc) of one rank's shard: row-parallel layers split K, the others split N."""
+    k, n = synth.LLAMA3_8B_SHAPES[name]
+    if world > 1 and ROW_PARALLEL[name]:
+        return k // world, n
+    if world > 1:
+        return k, n // world
+    return k, n
+
+
+def shard_layer(name: str, world: int, rank: int, dev: torch.device) -> synth.SynthLayer:
+    """The seeded master codes and scales of one rank's shard (any rank can draw any rank's shard)."""
+    si = list(synth.LLAMA3_8B_SHAPES).index(name)
+    k_loc, n_loc = shard_shape(name, world)
+    return synth.make_layer(n_loc, k_loc, GROUP, seed=100 * si + rank, sym=True, dtype=torch.float16, device=dev)
+
+
 def build_cells(world: int, rank: int, dev: torch.device):
     """Pack this rank's shard of every (shape, b) and allocate activations/outputs for every M."""
     from matgptq_b200 import ops  # noqa: F401
     weights = {}
     for si, (name, (k, n)) in enumerate(synth.LLAMA3_8B_SHAPES.items()):
-        if world > 1 and ROW_PARALLEL[name]:
-            k_loc, n_loc = k // world, n
-        elif world > 1:
-            k_loc, n_loc = k, n // world
-        else:
-            k_loc, n_loc = k, n
-        layer = synth.make_layer(n_loc, k_loc, GROUP, seed=100 * si + rank, sym=True, dtype=torch.float16, device=dev)
+        k_loc, n_loc = shard_shape(name, world)
+        layer = shard_layer(name, world, rank, dev)
         scales_r = torch.ops.matgptq_cuda.reorder_matgptq_scales(layer.scales, n_loc, k_loc, GROUP)
         for b in BITS:
             packed = torch.ops.matgptq_cuda.slice_pack_matgptq_qweights(layer.qweight, n_loc, k_loc, 8, b, GROUP, 1)
@@ -195,24 +211,37 @@ def build_cells(world: int, rank: int, dev: torch.device):
     return cells
 
 
-_PHASE = ["start"]
+_PHASE = ["start", time.monotonic()]  # current phase and when it began
 
 
 def progress(msg: str) -> None:
-    """Remember the phase (the watchdog reports it) and, with MATGPTQ_BENCH_VERBOSE=1, print it on stderr."""
+    """Remember the phase and its start (the watchdog reports both) and, with MATGPTQ_BENCH_VERBOSE=1, print it
+    on stderr."""
     _PHASE[0] = msg
+    _PHASE[1] = time.monotonic()
     if os.environ.get("MATGPTQ_BENCH_VERBOSE"):
         print(f"[bench rank {os.environ.get('RANK', '0')}] {msg}", file=sys.stderr, flush=True)
 
 
-def start_watchdog(seconds: float) -> None:
+def start_watchdog(stall_seconds: float, total_seconds: float) -> None:
     """A multi-rank run that stalls (a rank that never joins a collective, a communicator that never comes
-    up) would otherwise sit until somebody kills it: after `seconds` say where it stands and leave."""
+    up) would otherwise sit until somebody kills it.  When one phase lasts longer than `stall_seconds`, or
+    the whole run longer than `total_seconds`, print where it stands as one JSON line on stdout (a launcher's
+    traceback on stderr cannot bury it) and leave with exit code 3."""
+    t_start = time.monotonic()
+
     def bark():
-        time.sleep(seconds)
-        print(f"[bench rank {os.environ.get('RANK', '0')}] watchdog: no result after {seconds:.0f} s, "
-              f"last phase: {_PHASE[0]}", file=sys.stderr, flush=True)
-        os._exit(3)
+        while True:
+            time.sleep(1.0)
+            now = time.monotonic()
+            stalled = now - _PHASE[1] > stall_seconds
+            if stalled or now - t_start > total_seconds:
+                line = {"stalled": True, "rank": int(os.environ.get("RANK", "0")), "phase": _PHASE[0],
+                        "seconds_in_phase": round(now - _PHASE[1], 1), "seconds_total": round(now - t_start, 1),
+                        "why": "no progress" if stalled else "overall limit"}
+                print(json.dumps(line), flush=True)
+                print(f"[bench rank {line['rank']}] watchdog: {line['why']}, last phase: {_PHASE[0]}", file=sys.stderr, flush=True)
+                os._exit(3)
     threading.Thread(target=bark, daemon=True).start()
 
 
@@ -223,15 +252,54 @@ def launch_cell(c, flags: int, world: int):
         torch.distributed.all_reduce(c["y"])
 
 
+PARITY_TOLERANCE = 1e-2   # max|y - y_ref| / max|y_ref| against an fp32 accumulation over the oracle's weights
+PARITY_SAMPLE_ROWS = 256  # out-features checked per (shape, bitwidth): evenly spread over N
+
+
+def check_cells(cells, world: int, dev: torch.device) -> dict:
+    """Outside the timed region: compare what the sweep left in every cell's output with the oracle
+    (dequantise-then-matmul, fp32 accumulation) on a sample of out-features.  With several ranks, rank 0
+    checks the all-reduced outputs of the row-parallel cells against the sum over every rank's shard and
+    its own shard of the column-parallel ones.  Returns the worst relative error and the cell count."""
+    from oracle import matgptq_oracle as oracle
+    worst, checked, failed = 0.0, 0, []
+    ref_cache = {}
+    for c in cells:
+        key = (c["name"], c["b"])
+        if key not in ref_cache:
+            n_loc = c["n_loc"]
+            rows = torch.linspace(0, n_loc - 1, min(PARITY_SAMPLE_ROWS, n_loc)).long().unique()
+            ranks = range(world) if (world > 1 and ROW_PARALLEL[c["name"]]) else (0,)
+            shards = []
+            for r in ranks:
+                layer = shard_layer(c["name"], world, r, dev)
+                q, sc, z = layer.qweight[rows.to(dev)].cpu(), layer.scales[rows.to(dev)].cpu(), layer.zeros[rows.to(dev)].cpu()
+                shards.append(oracle.dequantize_weight(q, sc, z, 8, c["b"]))
+                del layer
+            ref_cache[key] = (rows, shards)
+        rows, shards = ref_cache[key]
+        x = c["x"].cpu()
+        y_ref = sum(oracle.linear_fp32_accumulate(x, w) for w in shards)
+        err = oracle.rel_err(c["y"][:, rows.to(dev)].cpu(), y_ref)
+        worst = max(worst, err)
+        checked += 1
+        if not err <= PARITY_TOLERANCE:
+            failed.append({"shape": c["name"], "m": c["m"], "b": c["b"], "rel_err": err})
+    return {"checked_cells": checked, "max_rel_err": round(worst, 6), "tolerance": PARITY_TOLERANCE,
+            "sample_rows": PARITY_SAMPLE_ROWS, "failed": failed[:8]}
+
+
 def per_cell_table(dev: torch.device, flags: int) -> dict:
     """Cold-L2 time of every cell on its own: a graph of launches cycling over enough copies of the
     cell's weights to exceed L2 several times over. Returns per-bitwidth and per-cell figures."""
     from matgptq_b200 import ops
     out_cells = []
+    peak, _ = measured_peaks()
     for si, (name, (k, n)) in enumerate(synth.LLAMA3_8B_SHAPES.items()):
         layer = synth.make_layer(n, k, GROUP, seed=100 * si, sym=True, dtype=torch.float16, device=dev)
         scales_r = torch.ops.matgptq_cuda.reorder_matgptq_scales(layer.scales, n, k, GROUP)
         for b in BITS:
+            progress(f"per-cell table: {name} b={b}")
             packed = torch.ops.matgptq_cuda.slice_pack_matgptq_qweights(layer.qweight, n, k, 8, b, GROUP, 1)
             wbytes = packed.numel() * 4
             copies = max(2, min(64, -(-512 * 1024 * 1024 // wbytes)))
@@ -279,7 +347,8 @@ def per_cell_table(dev: torch.device, flags: int) -> dict:
                         wt.append(e0.elapsed_time(e1) * 1e3 / 20)
                 nbytes = synth.algorithmic_bytes(n, k, m, b, GROUP)
                 out_cells.append({"shape": name, "k": k, "n": n, "m": m, "b": b, "us": round(us, 3),
-                                  "gbs": round(nbytes / us / 1e3, 1), "warm_l2_us": round(statistics.median(wt), 3)})
+                                  "gbs": round(nbytes / us / 1e3, 1), "frac": round(nbytes / us / 1e3 / peak, 3),
+                                  "warm_l2_us": round(statistics.median(wt), 3)})
                 del graph, warm
             del packs, scs, packed
         del layer
@@ -300,7 +369,7 @@ def ours_main(args) -> None:
     dev = torch.device("cuda", local_rank)
     torch.cuda.set_device(dev)
     if args.watchdog > 0:
-        start_watchdog(args.watchdog)
+        start_watchdog(args.watchdog, args.watchdog_total)
     if world > 1:
         progress("bringing the process group up")
         torch.distributed.init_process_group("nccl", device_id=dev)
@@ -327,15 +396,25 @@ def ours_main(args) -> None:
         sampler = ClockSampler(local_rank)
         if rank == 0:
             sampler.start()
-        # warm-up: at least W replays and at least 0.3 s under load, so that the clocks have
-        # ramped up and nvidia-smi has samples taken under the same load as the timed steps
-        t_warm = time.perf_counter()
+        # warm-up: at least W replays and about 0.3 s under load, so that the clocks have ramped up and
+        # nvidia-smi has samples taken under the same load as the timed steps.  With several ranks the graph
+        # holds all-reduces, so EVERY rank must replay it the same number of times: a count that each rank
+        # derives from its own clock lets one rank queue collectives that its peers never match.  The
+        # count is therefore a constant for world > 1 and only timed for a single rank.
         n_warm = 0
-        while n_warm < max(args.warmup, 3) or time.perf_counter() - t_warm < 0.3:
-            graph.replay()
-            n_warm += 1
-            if n_warm % 16 == 0:
-                stream.synchronize()
+        if world > 1:
+            for n_warm in range(1, max(args.warmup, 3, MULTI_RANK_WARMUP_REPLAYS) + 1):
+                graph.replay()
+                if n_warm % 16 == 0:
+                    stream.synchronize()
+                    progress(f"warm-up: {n_warm} replays")
+        else:
+            t_warm = time.perf_counter()
+            while n_warm < max(args.warmup, 3) or time.perf_counter() - t_warm < 0.3:
+                graph.replay()
+                n_warm += 1
+                if n_warm % 16 == 0:
+                    stream.synchronize()
         stream.synchronize()
         progress(f"warm-up done ({n_warm} replays)")
         if world > 1:
@@ -353,6 +432,10 @@ def ours_main(args) -> None:
         elapsed_ms = e0.elapsed_time(e1)
         progress(f"timed steps done: {elapsed_ms:.2f} ms")
         clocks = sampler.stop() if rank == 0 else None
+        parity = None
+        if rank == 0 and not args.no_check:
+            progress("checking the outputs of the sweep against the oracle")
+            parity = check_cells(cells, world, dev)
         # a live CUDA graph that holds NCCL kernels blocks the process group's shutdown
         graph.reset()
         del graph
@@ -395,6 +478,8 @@ def ours_main(args) -> None:
                    "cells_per_step": launches_per_step, "l2_policy": "inputs larger than L2: ~400 MB of other weights between reuses",
                    "parallelism": "tp%d" % world if world > 1 else "single", "pdl": not args.no_pdl},
         "clocks": clocks,
+        "parity_checked": bool(parity and parity["checked_cells"] == launches_per_step and not parity["failed"]),
+        "parity": parity,
         "gpu_launches": launches_per_step * args.steps,
         "roofline": {"bound": "hbm", "achieved": round(value / world, 2), "peak": peak, "unit": "GB/s",
                      "frac": round(value / world / peak, 4),
@@ -458,11 +543,14 @@ def run_tensor_core_cells(dev: torch.device) -> list:
     """Tensor-core regime: bf16, M in {32,64,128,256}, b in {3,4,8}, next to torch's dense bf16 GEMM on the
     dequantised weights.  Cold L2: launches rotate over copies of the weights."""
     from matgptq_b200 import ops
+    from oracle import matgptq_oracle as oracle
     out = []
     for si, (name, (k, n)) in enumerate(synth.LLAMA3_8B_SHAPES.items()):
         layer = synth.make_layer(n, k, GROUP, seed=300 + si, sym=True, dtype=torch.bfloat16, device=dev)
+        rows_dev = torch.linspace(0, n - 1, min(PARITY_SAMPLE_ROWS, n)).long().unique().to(dev)
         scales_r = torch.ops.matgptq_cuda.reorder_matgptq_scales(layer.scales, n, k, GROUP)
         for b in (3, 4, 8):
+            progress(f"tensor-core cells: {name} b={b}")
             packed = torch.ops.matgptq_cuda.slice_pack_matgptq_qweights(layer.qweight, n, k, 8, b, GROUP, 3)
             dense = torch.ops.matgptq_cuda.dequantize_matgptq(packed, scales_r, n, k, b, GROUP, 3)
             copies = max(2, min(16, -(-300 * 1024 * 1024 // (dense.numel() * 2))))
@@ -505,9 +593,17 @@ def run_tensor_core_cells(dev: torch.device) -> list:
                         times[label] = statistics.median(ts)
                         del graph
                 flops = 2.0 * m * n * k
+                # outside the timed region: this cell's output against the oracle on a sample of out-features
+                y.zero_()
+                ours(0)
+                torch.cuda.synchronize()
+                w_ref = oracle.dequantize_weight(layer.qweight[rows_dev].cpu(), layer.scales[rows_dev].cpu(),
+                                                 layer.zeros[rows_dev].cpu(), 8, b)
+                err = oracle.rel_err(y[:, rows_dev].cpu(), oracle.linear_fp32_accumulate(x.cpu(), w_ref))
                 out.append({"shape": name, "m": m, "b": b, "us": round(times["ours"], 2), "dense_bf16_us": round(times["dense"], 2),
                             "tflops": round(flops / times["ours"] / 1e6, 1),
-                            "gbs": round(synth.algorithmic_bytes(n, k, m, b, GROUP) / times["ours"] / 1e3, 1)})
+                            "gbs": round(synth.algorithmic_bytes(n, k, m, b, GROUP) / times["ours"] / 1e3, 1),
+                            "rel_err": round(err, 6), "parity_ok": bool(err <= PARITY_TOLERANCE)})
             del packs, denses
         del layer
     return out
@@ -572,7 +668,7 @@ def decode_main(args) -> None:
     dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
     torch.cuda.set_device(dev)
     if args.watchdog > 0:
-        start_watchdog(args.watchdog)
+        start_watchdog(args.watchdog, args.watchdog_total)
     if world > 1:
         progress("bringing the process group up")
         torch.distributed.init_process_group("nccl", device_id=dev)
@@ -595,9 +691,12 @@ def main() -> None:
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
-    ap.add_argument("--watchdog", type=float, default=600.0, help="seconds after which a stalled run reports its phase and exits 3 (0 = off)")
+    ap.add_argument("--watchdog", type=float, default=150.0,
+                    help="seconds one phase may last before the run reports where it stands and exits 3 (0 = off)")
+    ap.add_argument("--watchdog-total", type=float, default=900.0, help="the same for the whole run")
     ap.add_argument("--no-pdl", action="store_true", help="launch without programmatic dependent launch")
     ap.add_argument("--no-table", action="store_true", help="skip the per-cell cold-L2 table")
+    ap.add_argument("--no-check", action="store_true", help="skip the comparison of the sweep's outputs with the oracle")
     ap.add_argument("--no-decode", action="store_true", help="skip the whole-model decode measurement")
     ap.add_argument("--decode", type=str, default=None,
                     help="model:batch:prompt:new:bits[:layers] - only run this decode and exit; bits is the mean of a seeded "

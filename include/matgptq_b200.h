@@ -29,6 +29,7 @@ extern "C" {
 #define MATGPTQ_B200_ERR_UNSUPPORTED 3 /* valid in the reference but not provided here */
 #define MATGPTQ_B200_ERR_ALIGNMENT 4   /* a pointer is not 16-byte aligned */
 #define MATGPTQ_B200_ERR_SCRATCH_TOO_SMALL 5 /* the shape needs more scratch than the built-in array holds */
+#define MATGPTQ_B200_ERR_SCRATCH_UNAVAILABLE 6 /* the built-in scratch array could not be set up on this device */
 
 /* feature flags: bits 0 and 1 are the reference's (csrc/include/common.cuh:78-86,
  * matgptq_cuda/matgptq_linear.py:6-9); bit 2 is an addition. */
@@ -83,11 +84,7 @@ int matgptq_b200_matmul_tuned(int64_t bitwidth, int64_t group_size, int64_t n_ou
  * after it; one buffer per stream in flight).  Without scratch (workspace NULL, or
  * matgptq_b200_matmul) K is not split.
  *   path: 0 = choose by batch size (cluster GEMV below 32 rows, tensor cores from 32),
- *         1 = cluster GEMV, 2 = tensor-core path (any batch size),
- *         3 = persistent stream-K GEMV, batches 1..4 only, needs
- *             matgptq_b200_persistent_gemv_workspace_bytes() of scratch; status 3 when the shape
- *             or the scratch does not allow it.  Kept for experiments: on B200 it is slower
- *             than path 1 on the Llama-3-8B shapes.
+ *         1 = cluster GEMV, 2 = tensor-core path (any batch size)
  *   split_k: 0 = choose; otherwise the number of CTAs along K (tensor-core path: needs
  *            split_k*M*N*4 bytes of scratch)
  * The reference has one kernel pair for all batch sizes and no scratch
@@ -99,22 +96,26 @@ int matgptq_b200_matmul_ws(int64_t bitwidth, int64_t group_size, int64_t n_out, 
 
 /* Scratch bytes matgptq_b200_matmul_ws wants for this shape on the current device (0 = none). */
 int64_t matgptq_b200_matmul_workspace_bytes(int64_t n_out, int64_t n_in, int64_t batch);
-/* Scratch bytes of path 3 on the current device (independent of the shape). */
-int64_t matgptq_b200_persistent_gemv_workspace_bytes(void);
 
 /*
  * matgptq_b200_matmul_ws for callers that cannot allocate: hosts whose memory pool already
  * owns the whole device, plugins without access to their host's allocator, loops in which
  * cudaMalloc is forbidden because it synchronises the device.  The split-K scratch is a fixed
- * array of MATGPTQ_B200_STATIC_SCRATCH_BYTES inside the library image; it occupies that much
- * memory on every GPU that loads the library until the process exits.  This entry point has no
+ * array of MATGPTQ_B200_STATIC_SCRATCH_BYTES inside the library image; once set up on a GPU it
+ * occupies that much of its memory until the process exits.  This entry point has no
  * counterpart in the reference.
  *   - It calls no cudaMalloc, cudaFree or any other allocating routine.
  *   - Shapes whose scratch need (matgptq_b200_matmul_workspace_bytes) exceeds the array return
  *     MATGPTQ_B200_ERR_SCRATCH_TOO_SMALL and launch nothing.
  *   - The first call on a device that needs scratch resolves the array's device address
- *     (cudaGetSymbolAddress, with that device current) and remembers it; make that first call
- *     before any stream capture starts.
+ *     (cudaGetSymbolAddress, with that device current) and remembers it.  The CUDA runtime loads
+ *     device code lazily, so it is THIS first call that brings the array into the device's memory:
+ *     the driver takes the MATGPTQ_B200_STATIC_SCRATCH_BYTES then, not when the library is loaded.
+ *     Make that first call (any shape with a batch of 32 or more and few row tiles, e.g. the one you
+ *     will run) early: before a host that sizes its pool from the free memory does so, and before
+ *     any stream capture starts.  If the device has no room left at that moment the call returns
+ *     MATGPTQ_B200_ERR_SCRATCH_UNAVAILABLE and launches nothing.  Every later call on that device
+ *     leaves the amount of free device memory unchanged.
  *   - All calls on a device share the one array and it keeps whatever the last call left in it;
  *     nothing in it needs clearing, because each call writes every partial sum before reading
  *     it.  Two calls whose kernels overlap on the GPU (different streams) race on it: serialise
@@ -189,7 +190,7 @@ int matgptq_b200_silu_mul(const void *gate_up, void *out, int64_t rows, int64_t 
  * up records a non-zero code instead of hanging, and its output is then undefined.
  * This call synchronises with the device, returns the first code recorded on the
  * current device since the last reset (0 = none; 101 weight copy, 102 activation
- * copy, 103 tensor-core completion, 104 cross-CTA completion) and clears it when reset != 0.  The reference has
+ * copy, 103 tensor-core completion) and clears it when reset != 0.  The reference has
  * no counterpart: its only error path is exit(1) in CHECK_CUDA (csrc/include/common.cuh:44-51).
  */
 int matgptq_b200_device_status(int *status_out, int reset);

@@ -30,7 +30,6 @@ SIGNATURES = {
     "matgptq_b200_matmul_zp": (_c_int, [_c_i64, _c_i64, _c_i64, _c_i64, _c_i64, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_u32]),
     "matgptq_b200_matmul_tuned": (_c_int, [_c_i64, _c_i64, _c_i64, _c_i64, _c_i64, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_u32, _c_int, _c_int]),
     "matgptq_b200_matmul_ws": (_c_int, [_c_i64, _c_i64, _c_i64, _c_i64, _c_i64, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_u32, _c_ptr, _c_i64, _c_int, _c_int]),
-    "matgptq_b200_persistent_gemv_workspace_bytes": (_c_i64, []),
     "matgptq_b200_matmul_workspace_bytes": (_c_i64, [_c_i64, _c_i64, _c_i64]),
     "matgptq_b200_matmul_static_scratch": (_c_int, [_c_i64, _c_i64, _c_i64, _c_i64, _c_i64, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_u32]),
     "matgptq_b200_add_rmsnorm": (_c_int, [_c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_i64, _c_i64, ctypes.c_float, _c_u32, _c_ptr]),

@@ -39,6 +39,8 @@ const char *matgptq_b200_strerror(int status) {
     case MG_ERR_ALIGNMENT: return "pointer is not 16-byte aligned";
     case MATGPTQ_B200_ERR_SCRATCH_TOO_SMALL:
       return "this shape needs more split-K scratch than the built-in array holds: pass scratch through matgptq_b200_matmul_ws";
+    case MATGPTQ_B200_ERR_SCRATCH_UNAVAILABLE:
+      return "the built-in scratch array could not be set up on this device (no memory left for it when first used?)";
     default: return "unknown status";
   }
 }
@@ -58,7 +60,7 @@ static int matmul_impl(int64_t bitwidth, int64_t group_size, int64_t n_out, int6
                        int64_t workspace_bytes, int path, int warps_per_cta, int split_k, const void *z = nullptr) {
   const int st = check_shape(n_out, n_in, bitwidth, group_size);
   if (st != MG_OK) return st;
-  if (batch < 0 || batch > (1 << 24) || path < 0 || path > 3 || workspace_bytes < 0) return MG_ERR_BAD_ARG;
+  if (batch < 0 || batch > (1 << 24) || path < 0 || path > 2 || workspace_bytes < 0) return MG_ERR_BAD_ARG;
   if (batch == 0) return MG_OK;
   if (!w || !s || !x || !y) return MG_ERR_BAD_ARG;
   if (!aligned16(w) || !aligned16(x) || !aligned16(s) || !aligned16(z) || (reinterpret_cast<uintptr_t>(y) & 1u) ||
@@ -71,7 +73,7 @@ static int matmul_impl(int64_t bitwidth, int64_t group_size, int64_t n_out, int6
   int r;
   if (z) {
     // zero points: every batch size runs on the GEMV family (more than 16 rows in passes of 16); the tensor-core
-    // path and the persistent kernel have the implicit zero point only
+    // path has the implicit zero point only
     if (path > 1) return MG_ERR_UNSUPPORTED;
     r = mg::gemv_zp_launch(static_cast<int>(bitwidth), static_cast<int>(group_size), static_cast<int>(n_out),
                            static_cast<int>(n_in), static_cast<int>(batch), w, s, z, x, y, bf16, pdl, warps_per_cta, split_k, cs);
@@ -80,17 +82,8 @@ static int matmul_impl(int64_t bitwidth, int64_t group_size, int64_t n_out, int6
                            static_cast<int>(n_in), static_cast<int>(batch), w, s, x, y, workspace, workspace_bytes, bf16,
                            pdl, split_k, cs);
   } else {
-    // The persistent stream-K kernel runs only on request (path 3): measured on B200 it is slower than
-    // the cluster kernel on every Llama-3-8B shape (its cross-CTA completion and per-CTA set-up cost
-    // about 3 us per launch), so the automatic choice is the cluster kernel.
-    r = MG_ERR_UNSUPPORTED;
-    if (path == 3 && warps_per_cta == 0)
-      r = mg::gemv_stream_launch(static_cast<int>(bitwidth), static_cast<int>(group_size), static_cast<int>(n_out),
-                                 static_cast<int>(n_in), static_cast<int>(batch), w, s, x, y, workspace, workspace_bytes,
-                                 bf16, pdl, cs);
-    if (r == MG_ERR_UNSUPPORTED && path != 3)
-      r = mg::gemv_launch(static_cast<int>(bitwidth), static_cast<int>(group_size), static_cast<int>(n_out),
-                          static_cast<int>(n_in), static_cast<int>(batch), w, s, nullptr, x, y, bf16, pdl, warps_per_cta, split_k, cs);
+    r = mg::gemv_launch(static_cast<int>(bitwidth), static_cast<int>(group_size), static_cast<int>(n_out),
+                        static_cast<int>(n_in), static_cast<int>(batch), w, s, nullptr, x, y, bf16, pdl, warps_per_cta, split_k, cs);
   }
   if (r != MG_OK) return r;
   if (!(flags & MATGPTQ_B200_FLAG_ASYNC)) {
@@ -123,12 +116,6 @@ int matgptq_b200_matmul_ws(int64_t bitwidth, int64_t group_size, int64_t n_out, 
                            void *workspace, int64_t workspace_bytes, int path, int split_k) {
   return matmul_impl(bitwidth, group_size, n_out, n_in, batch, w, s, x, y, stream, flags, workspace, workspace_bytes, path,
                      0, split_k);
-}
-
-int64_t matgptq_b200_persistent_gemv_workspace_bytes(void) {
-  int sms = 0;
-  if (sm_count_of_current_device(&sms) != MG_OK) sms = 148;
-  return mg::gemv_stream_workspace_bytes(sms);
 }
 
 int64_t matgptq_b200_matmul_workspace_bytes(int64_t n_out, int64_t n_in, int64_t batch) {
@@ -212,12 +199,10 @@ int matgptq_b200_device_status(int *status_out, int reset) {
   if (r != MG_OK) return r;
   r = mg::gemm_tc_device_status(&b, reset);
   if (r != MG_OK) return r;
-  int c = 0, d = 0;
-  r = mg::gemv_stream_device_status(&c, reset);
-  if (r != MG_OK) return r;
+  int d = 0;
   r = mg::gemv_zp_device_status(&d, reset);
   if (r != MG_OK) return r;
-  if (status_out) *status_out = a ? a : (b ? b : (c ? c : d));
+  if (status_out) *status_out = a ? a : (b ? b : d);
   return MG_OK;
 }
 

@@ -28,6 +28,7 @@
 
 #include "async.cuh"
 #include "decode.cuh"
+#include "host_util.h"
 #include "kernels.h"
 
 namespace mg {
@@ -417,13 +418,14 @@ static int make_x_tensor_map(CUtensorMap *map, const void *x, int M, int K, int 
   typedef CUresult (*EncodeTiled)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
                                   const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-  static EncodeTiled encode = nullptr;
-  if (!encode) {
+  // looked up once; the initialisation of a function-local static is thread-safe
+  static const EncodeTiled encode = []() -> EncodeTiled {
     void *fn = nullptr;
     cudaDriverEntryPointQueryResult q;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q) != cudaSuccess || !fn) return MG_ERR_CUDA;
-    encode = reinterpret_cast<EncodeTiled>(fn);
-  }
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q) != cudaSuccess) return nullptr;
+    return reinterpret_cast<EncodeTiled>(fn);
+  }();
+  if (!encode) return MG_ERR_CUDA;
   const cuuint64_t gdim[2] = {static_cast<cuuint64_t>(K), static_cast<cuuint64_t>(M)};
   const cuuint64_t gstride[1] = {static_cast<cuuint64_t>(K) * 2};
   const cuuint32_t box[2] = {64u, static_cast<cuuint32_t>(box_rows)};
@@ -448,13 +450,10 @@ static int launch_gemm_tc(GemmParams p, cudaStream_t stream, bool pdl) {
   }
   p.stages = stages;
   const TcPlan plan = tc_plan(p.ncols, stages);
-  static bool opted_in[64] = {};
-  int dev = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess) return MG_ERR_CUDA;
-  if (dev < 0 || dev >= 64) return MG_ERR_BAD_ARG;
-  if (!opted_in[dev]) {
-    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 224 * 1024) != cudaSuccess) return MG_ERR_CUDA;
-    opted_in[dev] = true;
+  static SharedMemoryOptIn opt_in;  // one per instantiation of this launcher
+  {
+    const int st = opt_in.ensure(kernel, 224 * 1024);
+    if (st != MG_OK) return st;
   }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((p.N + 127) / 128, p.split, (p.M + 255) / 256);
@@ -510,11 +509,10 @@ static int launch_gemm_tc_group(const GemmParams &p, int group_size, bool bf16, 
 int gemm_tc_launch(int bitwidth, int group_size, int N, int K, int M, const void *w, const void *s, const void *x,
                    void *y, void *workspace, long long workspace_bytes, bool bf16, bool pdl, int split_override,
                    cudaStream_t stream) {
-  static int sm_count = 0;
-  if (sm_count == 0) {
-    int dev = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess) return MG_ERR_CUDA;
-    if (cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return MG_ERR_CUDA;
+  int sm_count = 0;  // of the current device: the same value matgptq_b200_matmul_workspace_bytes sized the scratch with
+  {
+    const int st = current_device_sm_count(&sm_count);
+    if (st != MG_OK) return st;
   }
   GemmParams p;
   p.w = static_cast<const uint32_t *>(w);

@@ -34,6 +34,7 @@
 #include "async.cuh"
 #include "decode.cuh"
 #include "gemv_common.cuh"
+#include "host_util.h"
 #include "kernels.h"
 
 namespace cg = cooperative_groups;
@@ -560,8 +561,6 @@ __global__ void __launch_bounds__(512, 1) gemv_kernel(const GemvParams p) {
 // ----------------------------------------------------------------------------
 // host side
 // ----------------------------------------------------------------------------
-static int g_sm_count = 0;
-
 // Shared memory per CTA that leaves room for exactly `ctas` CTAs on an SM (227 KB usable, 1 KB reserved per CTA).
 static inline int smem_for_ctas_per_sm(int ctas) { return (227 * 1024) / ctas - 1024; }
 
@@ -593,15 +592,9 @@ static int launch_gemv(GemvParams p, int R, cudaStream_t stream, bool pdl) {
   const int floor_bytes = smem_for_ctas_per_sm(ctas_per_sm + 1) + 1;
   const size_t smem = static_cast<size_t>(plan.total > floor_bytes ? plan.total : floor_bytes);
   if (smem > 48 * 1024) {
-    static bool opted_in[64] = {};
-    int dev = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess) return MG_ERR_CUDA;
-    if (dev < 0 || dev >= 64) return MG_ERR_BAD_ARG;
-    if (!opted_in[dev]) {
-      cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024);
-      if (e != cudaSuccess) return MG_ERR_CUDA;
-      opted_in[dev] = true;
-    }
+    static SharedMemoryOptIn opt_in;  // one per instantiation of this launcher
+    const int st = opt_in.ensure(kernel, 226 * 1024);
+    if (st != MG_OK) return st;
   }
   const int Rt = R / p.kslices;
   const int row_groups = (p.tiles + Rt - 1) / Rt;
@@ -712,10 +705,10 @@ static int launch_shape(GemvParams p, const GemvShape &c, int bitwidth, int grou
 int MG_GEMV_LAUNCH(int bitwidth, int group_size, int N, int K, int M, const void *w, const void *s, const void *z,
                    const void *x, void *y, bool bf16, bool pdl, int R_override, int S_override, cudaStream_t stream) {
   if (kZP != (z != nullptr)) return MG_ERR_BAD_ARG;
-  if (g_sm_count == 0) {
-    int dev = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess) return MG_ERR_CUDA;
-    if (cudaDeviceGetAttribute(&g_sm_count, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return MG_ERR_CUDA;
+  int sm_count = 0;
+  {
+    const int st = current_device_sm_count(&sm_count);
+    if (st != MG_OK) return st;
   }
   GemvParams p;
   p.w = static_cast<const uint32_t *>(w);
@@ -729,7 +722,7 @@ int MG_GEMV_LAUNCH(int bitwidth, int group_size, int N, int K, int M, const void
   p.tiles = N / 16;
   p.kblocks = K / 128;
   GemvShape first, second;
-  gemv_pick_config(p.tiles, p.kblocks, M < 16 ? M : 16, g_sm_count, &first, &second);
+  gemv_pick_config(p.tiles, p.kblocks, M < 16 ? M : 16, sm_count, &first, &second);
   if (R_override > 0 || S_override > 0) {
     // forced shape.  warps: low byte = warps per CTA, next byte = K slices inside the CTA (0 means 1)
     GemvShape forced = second;

@@ -23,12 +23,6 @@ int gemv_zp_launch(int bitwidth, int group_size, int N, int K, int M, const void
 int gemv_device_status(int *status_out, int reset);
 int gemv_zp_device_status(int *status_out, int reset);
 
-// gemv_stream.cu
-long long gemv_stream_workspace_bytes(int sm_count);
-int gemv_stream_launch(int bitwidth, int group_size, int N, int K, int M, const void *w, const void *s, const void *x,
-                       void *y, void *workspace, long long workspace_bytes, bool bf16, bool pdl, cudaStream_t stream);
-int gemv_stream_device_status(int *status_out, int reset);
-
 // gemm_tc.cu
 int gemm_tc_pick_split(int N, int K, int M, int sm_count);
 long long gemm_tc_workspace_bytes(int N, int K, int M, int sm_count);

@@ -6,8 +6,12 @@
 // serving process whose memory pool was sized up front and already owns the whole device, a
 // plugin called from inside such a host without access to its allocator, or a latency-critical
 // loop in which cudaMalloc (which synchronises the device) is forbidden.  For them the scratch
-// lives in the library image itself: a fixed array in device global memory that exists on
-// every GPU that loads the library, from load until the process exits.
+// lives in the library image itself: a fixed array in device global memory.  The CUDA runtime
+// loads device code lazily and this file has no kernel of its own, so the array comes into a
+// GPU's memory when its address is first asked for on that GPU (the first call below that needs
+// scratch there), and stays until the process exits.  That first call is the only one that can
+// change the amount of free device memory; it has to come before the host hands the rest of
+// the device to its pool.
 #include <cuda_runtime.h>
 
 #include <mutex>
@@ -22,7 +26,7 @@ namespace {
 constexpr long long kStaticScratchBytes = MATGPTQ_B200_STATIC_SCRATCH_BYTES;
 static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
 
-constexpr int kMaxDevices = 64;
+constexpr int kMaxDevices = 64;  // devices beyond this index are refused (bad argument)
 std::mutex g_setup_mutex;
 void *g_scratch_address[kMaxDevices] = {};
 bool g_scratch_ready[kMaxDevices] = {};
@@ -35,7 +39,11 @@ int static_scratch_address(void **out) {
   std::lock_guard<std::mutex> lock(g_setup_mutex);
   if (!g_scratch_ready[dev]) {
     void *ptr = nullptr;
-    if (cudaGetSymbolAddress(&ptr, g_static_scratch) != cudaSuccess || ptr == nullptr) return MG_ERR_CUDA;
+    // loads this module on the device if it is not there yet: the driver takes the array's bytes now
+    if (cudaGetSymbolAddress(&ptr, g_static_scratch) != cudaSuccess || ptr == nullptr) {
+      (void)cudaGetLastError();  // the failure is reported through the status code, not left pending
+      return MATGPTQ_B200_ERR_SCRATCH_UNAVAILABLE;
+    }
     g_scratch_address[dev] = ptr;
     g_scratch_ready[dev] = true;
   }

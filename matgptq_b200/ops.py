@@ -310,8 +310,6 @@ def matmul_matgptq_raw(x: torch.Tensor, packed: torch.Tensor, scales: torch.Tens
                 need = split_k * batch * n_out * 4
             elif path == 2:
                 need = _lib.matgptq_b200_matmul_workspace_bytes(n_out, n_in, max(batch, 32))
-            elif path == 3:
-                need = _lib.matgptq_b200_persistent_gemv_workspace_bytes()
             else:
                 need = _lib.matgptq_b200_matmul_workspace_bytes(n_out, n_in, batch)
             if need > 0:

@@ -155,64 +155,6 @@ def test_input_views_and_errors(cuda):
     assert empty.shape == (0, n_out)
 
 
-@pytest.mark.parametrize("b", BITS)
-@pytest.mark.parametrize("gs", [-1, 32, 128])
-@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
-@pytest.mark.parametrize("m", [1, 3, 4])
-def test_persistent_gemv_ragged(cuda, b, gs, dtype, m):
-    """The persistent stream-K kernel (batches 1..4) on a shape where nothing divides evenly."""
-    from matgptq_b200 import _native, ops
-    n_out, n_in = 208, 1152
-    packed, scales_r, w_ref, flag = _layer_and_ref(n_out, n_in, gs, b, dtype, 3, cuda)
-    x = synth.make_activations(m, n_in, seed=m, dtype=dtype, device=cuda)
-    y = ops.matmul_matgptq_raw(x, packed, scales_r, n_out, n_in, b, gs, flag, path=3)
-    assert _native.device_status() == 0
-    assert oracle.rel_err(y.cpu(), oracle.linear_fp32_accumulate(x.cpu(), w_ref)) <= TOL
-
-
-@pytest.mark.parametrize("b", BITS)
-@pytest.mark.parametrize("shape", [(4096, 4096), (4096, 1024), (4096, 14336), (14336, 4096)])
-@pytest.mark.parametrize("m", [1, 4])
-def test_persistent_gemv_llama_shapes(cuda, b, shape, m):
-    """Tiles that span CTAs are completed across CTAs; reusing one scratch buffer over many launches,
-    eagerly and from a replayed CUDA graph, keeps giving the cluster kernel's answer."""
-    from matgptq_b200 import _native, ops
-    n_in, n_out = shape
-    packed, scales_r, _, flag = _layer_and_ref(n_out, n_in, 128, b, torch.float16, 5, cuda)
-    need = _native.load().matgptq_b200_persistent_gemv_workspace_bytes()
-    assert need > 0
-    ws = torch.randint(0, 255, (need,), dtype=torch.uint8, device=cuda)  # arbitrary contents are allowed
-    xs = [synth.make_activations(m, n_in, seed=s, dtype=torch.float16, device=cuda) for s in range(3)]
-    refs = [ops.matmul_matgptq_raw(x, packed, scales_r, n_out, n_in, b, 128, flag, path=1) for x in xs]
-    if m * n_in * 2 > 96 * 1024:
-        # four rows of 14336 activations do not fit beside the rings: forcing the kernel is refused
-        # (path 0 would quietly take the cluster kernel instead)
-        with pytest.raises(RuntimeError, match="status 3"):
-            ops.matmul_matgptq_raw(xs[0], packed, scales_r, n_out, n_in, b, 128, flag, path=3, workspace=ws)
-        y = ops.matmul_matgptq_raw(xs[0], packed, scales_r, n_out, n_in, b, 128, flag, path=0, workspace=ws)
-        assert torch.equal(y, refs[0])
-        return
-    for x, ref in zip(xs, refs):
-        y = ops.matmul_matgptq_raw(x, packed, scales_r, n_out, n_in, b, 128, flag | 4, path=3, workspace=ws)
-        assert oracle.rel_err(y.float().cpu(), ref.float().cpu()) <= 2e-3
-    # graph replay: the same launch (same epoch) three times with changing activations
-    xg = xs[0].clone()
-    yg = torch.empty(m, n_out, dtype=torch.float16, device=cuda)
-    stream = torch.cuda.Stream()
-    with torch.cuda.stream(stream):
-        ops.matmul_matgptq_raw(xg, packed, scales_r, n_out, n_in, b, 128, flag, out=yg, path=3, workspace=ws)
-        stream.synchronize()
-        graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph, stream=stream):
-            ops.matmul_matgptq_raw(xg, packed, scales_r, n_out, n_in, b, 128, flag, out=yg, path=3, workspace=ws)
-        for x, ref in zip(xs, refs):
-            xg.copy_(x)
-            graph.replay()
-            stream.synchronize()
-            assert oracle.rel_err(yg.float().cpu(), ref.float().cpu()) <= 2e-3
-    assert _native.device_status() == 0
-
-
 # ---- extension: per-group zero points (asymmetric quantisation) ---------------------------------------------
 
 def _asym_layer_and_ref(n_out, n_in, gs, b, dtype, seed, cuda):

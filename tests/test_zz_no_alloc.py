@@ -67,6 +67,34 @@ def test_static_scratch_matches_caller_scratch_twice_in_a_row(lib, cuda):
     assert _native.device_status() == 0
 
 
+def test_static_scratch_later_calls_leave_free_memory_unchanged(lib, cuda):
+    """Only the first call that needs scratch on a device may change the free device memory (it brings the
+    built-in array in); the calls after it must not, which is what a host whose pool owns the rest of the
+    device relies on.  Inputs and outputs are allocated before the measurement starts."""
+    n_in, n_out, b, m = 4096, 1024, 4, 64
+    packed, scales_r, flag = _layer(n_out, n_in, b, torch.float16, 5, cuda)
+    x = synth.make_activations(m, n_in, seed=5, dtype=torch.float16, device=cuda)
+    y = torch.empty(m, n_out, dtype=torch.float16, device=cuda)
+    stream = torch.cuda.current_stream().cuda_stream
+    assert lib.matgptq_b200_matmul_workspace_bytes(n_out, n_in, m) > 0
+
+    def call():
+        st = lib.matgptq_b200_matmul_static_scratch(b, 128, n_out, n_in, m, packed.data_ptr(), scales_r.data_ptr(),
+                                                    x.data_ptr(), y.data_ptr(), stream, flag)
+        assert st == 0
+        torch.cuda.synchronize()
+
+    call()  # set-up (if no earlier test did it) happens here
+    free_before, _ = torch.cuda.mem_get_info(cuda)
+    first = y.clone()
+    free_before, _ = torch.cuda.mem_get_info(cuda)  # taken after the clone: nothing below allocates through torch
+    call()
+    call()
+    free_after, _ = torch.cuda.mem_get_info(cuda)
+    assert free_after == free_before
+    assert torch.equal(y, first)
+
+
 def test_static_scratch_small_batches_and_limit(lib, cuda):
     n_in, n_out, b = 4096, 4096, 4
     packed, scales_r, flag = _layer(n_out, n_in, b, torch.float16, 3, cuda)
