@@ -195,6 +195,14 @@ int matgptq_b200_silu_mul(const void *gate_up, void *out, int64_t rows, int64_t 
  */
 int matgptq_b200_device_status(int *status_out, int reset);
 
+/*
+ * Self-test of that mechanism: launches one warp that waits, with a short poll limit, on a barrier that
+ * nothing will ever complete, so the wait runs out, `status_code` (101, 102 or 103) is recorded for
+ * matgptq_b200_device_status to report and *gave_up_flag (device int, may be NULL) is set to 1.  The kernel
+ * then ends normally; the device is not faulted or hung.  No counterpart in the reference.
+ */
+int matgptq_b200_selftest_wait_timeout(int status_code, int *gave_up_flag, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -42,6 +42,7 @@ SIGNATURES = {
     "matgptq_b200_reorder_scales": (_c_int, [_c_ptr, _c_ptr, _c_i64, _c_i64, _c_i64, _c_ptr]),
     "matgptq_b200_reorder_scales_host": (_c_int, [_c_ptr, _c_ptr, _c_i64, _c_i64, _c_i64]),
     "matgptq_b200_device_status": (_c_int, [ctypes.POINTER(ctypes.c_int), _c_int]),
+    "matgptq_b200_selftest_wait_timeout": (_c_int, [_c_int, _c_ptr, _c_ptr]),
     "matgptq_b200_dequantize": (_c_int, [_c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_i64, _c_i64, _c_int, _c_i64, _c_u32, _c_ptr]),
 }
 

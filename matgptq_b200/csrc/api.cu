@@ -202,7 +202,10 @@ int matgptq_b200_device_status(int *status_out, int reset) {
   int d = 0;
   r = mg::gemv_zp_device_status(&d, reset);
   if (r != MG_OK) return r;
-  if (status_out) *status_out = a ? a : (b ? b : d);
+  int e = 0;
+  r = mg::selftest_device_status(&e, reset);
+  if (r != MG_OK) return r;
+  if (status_out) *status_out = a ? a : (b ? b : (d ? d : e));
   return MG_OK;
 }
 

@@ -69,13 +69,18 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   return ok != 0;
 }
 
-// The rare path of mbar_wait, kept out of line so that the loops that wait stay small.
-static __device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity) {
-  for (uint32_t it = 0; it < kWaitPolls; ++it) {
+// Polls at most `polls` times; false when the phase did not complete.
+static __device__ __noinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity, uint32_t polls) {
+  for (uint32_t it = 0; it < polls; ++it) {
     if (mbar_try_wait(bar, parity)) return true;
     if (it > 4) __nanosleep(40);  // waiting warps should not take issue slots from working ones
   }
   return false;
+}
+
+// The rare path of mbar_wait, kept out of line so that the loops that wait stay small.
+static __device__ __forceinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity) {
+  return mbar_wait_bounded(bar, parity, kWaitPolls);
 }
 
 // Returns false when the phase did not complete within kWaitPolls polls.  try_wait itself blocks for a

@@ -167,7 +167,7 @@ __device__ __forceinline__ uint32_t dequant_pair(uint32_t v, uint16_t scale, boo
 }
 
 // Dense-weight tiles of the tensor-core path: pair P of a lane as s * (code - Z) * 2^(8-b), bit-exact with
-// dequant_pair(decode_pair(..)) for finite scales, in three instructions for fp16 (LOP3, HFMA2, HMUL2).  The
+// dequant_pair(decode_pair(..)), in three instructions for fp16 (LOP3, HFMA2, HMUL2).  The
 // HFMA2 turns 1024 + code*2^p straight into the exact integer (code - Z) * kDensePre; the rest of 2^(8-b)
 // (a factor 2, for b = 2 only, where (1024 + Z) * 64 would leave the fp16 range) is folded into the scale by
 // dense_scale().  The product is rounded once, as in dequantize() (src/quant_utils_matgpqt.py:19-22).
@@ -175,16 +175,21 @@ template <int B> struct DensePre {
   static constexpr int value = (B == 2) ? 32 : (1 << (8 - B));
 };
 
+// A finite scale whose multiple leaves the finite range is clamped to the largest finite value instead of
+// becoming infinite: times a code off the zero point the product overflows to the same infinity that
+// dequantize() gives, and times the code on the zero point it stays zero (infinity would make it NaN).
 template <int B, bool BF16> __device__ __forceinline__ uint32_t dense_scale(uint16_t scale) {
   constexpr float rest = static_cast<float>((1 << (8 - B)) / DensePre<B>::value);
   if constexpr (rest == 1.f) return splat16(scale);
+  constexpr uint16_t kInf = BF16 ? 0x7F80u : 0x7C00u;
+  uint16_t r;
   if constexpr (BF16) {
-    const __nv_bfloat16 v = __hmul(__ushort_as_bfloat16(scale), __float2bfloat16_rn(rest));
-    return splat16(__bfloat16_as_ushort(v));
+    r = __bfloat16_as_ushort(__hmul(__ushort_as_bfloat16(scale), __float2bfloat16_rn(rest)));
   } else {
-    const __half v = __hmul(__ushort_as_half(scale), __float2half_rn(rest));
-    return splat16(__half_as_ushort(v));
+    r = __half_as_ushort(__hmul(__ushort_as_half(scale), __float2half_rn(rest)));
   }
+  if ((r & 0x7FFFu) == kInf && (scale & 0x7FFFu) != kInf) r -= 1;  // largest finite value of the same sign
+  return splat16(r);
 }
 
 template <int B, int P_OFF> __device__ __forceinline__ uint32_t dense_int_at(uint32_t x) {

@@ -31,6 +31,9 @@ int gemm_tc_launch(int bitwidth, int group_size, int N, int K, int M, const void
                    cudaStream_t stream);
 int gemm_tc_device_status(int *status_out, int reset);
 
+// selftest.cu
+int selftest_device_status(int *status_out, int reset);
+
 // pack.cu
 int slice_launch(const uint8_t *in, uint8_t *out, long long numel, int master_bitwidth, int bitwidth,
                  cudaStream_t stream);

@@ -40,8 +40,38 @@ class MatGPTQLinear(torch.nn.Module):
                 scales, self.n_out_features, self.n_in_features, self.group_size),
             requires_grad=False)
 
+    @classmethod
+    def from_master(cls, qweight_master: torch.Tensor, scales: torch.Tensor, master_bitwidth: int, bitwidth: int,
+                    group_size: int) -> "MatGPTQLinear":
+        """Addition: build the layer from UNSLICED master codes; the MSB slicing of
+        ``matryoshka_slice`` (``src/quant_utils_matgpqt.py:9-17``) is fused into the GPU packer instead of
+        being a separate pass (``inference_demo_transformers.py:30-39``)."""
+        self = cls.__new__(cls)
+        torch.nn.Module.__init__(self)
+        self.n_out_features, self.n_in_features = qweight_master.shape
+        self.bitwidth, self.group_size = bitwidth, group_size
+        self.flag = MatGTPQ_FeatureFlags.ASYNC + MatGTPQ_FeatureFlags.IS_BF16 * (scales.dtype == torch.bfloat16)
+        self.matgptq_qweight = torch.nn.Parameter(
+            torch.ops.matgptq_cuda.slice_pack_matgptq_qweights(
+                qweight_master.contiguous(), self.n_out_features, self.n_in_features, master_bitwidth, bitwidth,
+                group_size, self.flag),
+            requires_grad=False)
+        self.matgptq_scales = torch.nn.Parameter(
+            torch.ops.matgptq_cuda.reorder_matgptq_scales(
+                scales.contiguous(), self.n_out_features, self.n_in_features, group_size),
+            requires_grad=False)
+        return self
+
     @torch.no_grad()
     def forward(self, x: torch.Tensor) -> torch.Tensor:
+        if x.dim() > 2:
+            # The reference hands the tensor to the operator as it is, which reads the last two dimensions
+            # only and returns [M, N] (csrc/bindings.cpp:171-174): right for a leading dimension of 1, wrong
+            # beyond.  Here every leading dimension counts as rows and the result keeps them.
+            y = torch.ops.matgptq_cuda.matmul_matgptq(
+                x.reshape(-1, self.n_in_features), self.matgptq_qweight, self.matgptq_scales, self.n_out_features,
+                self.n_in_features, self.bitwidth, self.group_size, self.flag)
+            return y.view(*x.shape[:-1], self.n_out_features)
         return torch.ops.matgptq_cuda.matmul_matgptq(
             x, self.matgptq_qweight, self.matgptq_scales, self.n_out_features, self.n_in_features,
             self.bitwidth, self.group_size, self.flag)

@@ -110,10 +110,7 @@ def _slice_pack_fake(qweights, n_out_features, n_in_features, master_bitwidth, b
     return qweights.new_empty((bitwidth * n_out_features * n_in_features // 32,), dtype=torch.uint32)
 
 
-@torch.library.custom_op("matgptq_cuda::reorder_matgptq_scales", mutates_args=())
-def reorder_matgptq_scales(scales: torch.Tensor, m: int, n: int, group_size: int) -> torch.Tensor:
-    """Reorder scales ``[N, G]`` for the kernels; same shape and dtype, on CUDA
-    (``m`` = out features, ``n`` = in features, as in the reference)."""
+def _reorder_impl(scales: torch.Tensor, m: int, n: int, group_size: int) -> torch.Tensor:
     # csrc/bindings.cpp:92-97
     if not scales.is_contiguous():
         raise RuntimeError("scales must be contiguous")
@@ -134,6 +131,13 @@ def reorder_matgptq_scales(scales: torch.Tensor, m: int, n: int, group_size: int
         if src is not scales:
             src.record_stream(torch.cuda.current_stream(dev))
     return out
+
+
+@torch.library.custom_op("matgptq_cuda::reorder_matgptq_scales", mutates_args=())
+def reorder_matgptq_scales(scales: torch.Tensor, m: int, n: int, group_size: int) -> torch.Tensor:
+    """Reorder scales ``[N, G]`` for the kernels; same shape and dtype, on CUDA
+    (``m`` = out features, ``n`` = in features, as in the reference)."""
+    return _reorder_impl(scales, m, n, group_size)
 
 
 @reorder_matgptq_scales.register_fake
@@ -161,19 +165,8 @@ def _check_matmul_args(input, matgptq_weights, matgptq_scales, n_out_features, n
         raise RuntimeError("input must have shape [..., M, n_in_features]")
 
 
-@torch.library.custom_op("matgptq_cuda::matmul_matgptq", mutates_args=())
-def matmul_matgptq(
-    input: torch.Tensor,
-    matgptq_weights: torch.Tensor,
-    matgptq_scales: torch.Tensor,
-    n_out_features: int,
-    n_in_features: int,
-    bitwidth: int,
-    group_size: int,
-    feature_flag: int,
-) -> torch.Tensor:
-    """``y[M, N] = x[M, K] @ Wdq.T`` for packed b-bit weights; ``M = input.size(-2)``.
-    Output is float16, or bfloat16 when ``feature_flag & 2``."""
+def _matmul_impl(input: torch.Tensor, matgptq_weights: torch.Tensor, matgptq_scales: torch.Tensor, n_out_features: int,
+                 n_in_features: int, bitwidth: int, group_size: int, feature_flag: int) -> torch.Tensor:
     _check_matmul_args(input, matgptq_weights, matgptq_scales, n_out_features, n_in_features, bitwidth, group_size)
     bf16 = bool(feature_flag & _native.FLAG_BF16)
     dtype = torch.bfloat16 if bf16 else torch.float16
@@ -199,6 +192,23 @@ def matmul_matgptq(
                                          ws.data_ptr() if ws is not None else None, ws_bytes, 0, 0)
         _native.check(st, "matmul_matgptq")
     return out
+
+
+@torch.library.custom_op("matgptq_cuda::matmul_matgptq", mutates_args=())
+def matmul_matgptq(
+    input: torch.Tensor,
+    matgptq_weights: torch.Tensor,
+    matgptq_scales: torch.Tensor,
+    n_out_features: int,
+    n_in_features: int,
+    bitwidth: int,
+    group_size: int,
+    feature_flag: int,
+) -> torch.Tensor:
+    """``y[M, N] = x[M, K] @ Wdq.T`` for packed b-bit weights; ``M = input.size(-2)``.
+    Output is float16, or bfloat16 when ``feature_flag & 2``."""
+    return _matmul_impl(input, matgptq_weights, matgptq_scales, n_out_features, n_in_features, bitwidth, group_size,
+                        feature_flag)
 
 
 @matmul_matgptq.register_fake

@@ -129,6 +129,17 @@ def rel_err(y: torch.Tensor, y_ref32: torch.Tensor) -> float:
     return (y.float() - y_ref32).abs().max().item() / denom
 
 
+def elementwise_err(y: torch.Tensor, y_ref32: torch.Tensor, rtol: float = 1e-2, atol_rms: float = 1e-2) -> float:
+    """Element-wise companion of ``rel_err``: the largest ``|y - y_ref| / (rtol*|y_ref| + atol)`` with the
+    absolute floor ``atol = atol_rms * rms(y_ref)``; a value <= 1 means every element is within
+    ``rtol`` relative error or within the floor.  The floor is needed because sums of thousands of
+    products land arbitrarily close to zero, where no relative bound on a single element is meaningful."""
+    ref = y_ref32.float()
+    atol = atol_rms * ref.pow(2).mean().sqrt().item()
+    bound = rtol * ref.abs() + max(atol, 1e-30)
+    return ((y.float() - ref).abs() / bound).max().item()
+
+
 # --------------------------------------------------------------------------- #
 # quantiser parameters (used only to build synthetic master codes)
 # --------------------------------------------------------------------------- #

@@ -56,6 +56,36 @@ def test_small_model_matches_dense_reference(cuda, dtype, batch):
     assert a["decode_s"] > 0 and a["prefill_s"] > 0
 
 
+@pytest.mark.gpu
+@pytest.mark.parametrize("batch", [1, 8])
+def test_full_width_layers_match_dense_reference(cuda, batch):
+    """Two decoder layers at the full width of the Llama-3.1-8B architecture (hidden 4096, MLP 14336, 32 heads
+    / 8 KV heads; small vocabulary), seeded per-layer bitwidths with mean 3 bits: the logits of the prefill
+    AND of the first decode step (one row per sequence: the GEMV launch shapes of the timed decode) against
+    the same model over the oracle's dequantised dense weights."""
+    from matgptq_b200 import decode
+    shape = decode.LlamaShape(4096, 14336, 32, 8, 2, 4096)
+    bits = decode.mixed_bitwidths(shape, 3.0, seed=0)
+    model = decode.PackedLlama(shape, bits, dtype=torch.float16, batch=batch, max_seq=64, device=cuda, keep_master=True, seed=0)
+    g = torch.Generator().manual_seed(1)
+    prompt = torch.randint(0, shape.vocab, (batch, 32), generator=g).to(cuda)
+    nxt = torch.randint(0, shape.vocab, (batch, 1), generator=g).to(cuda)
+    pos, pos1 = torch.arange(32, device=cuda), torch.tensor([32], device=cuda)
+
+    def run():
+        for k in model.k_cache + model.v_cache:
+            k.zero_()
+        return model.forward(prompt, pos), model.forward(nxt, pos1)
+
+    got_prefill, got_step = run()
+    packed_linear = model.linear
+    model.linear = _dense_linear_factory(model)
+    ref_prefill, ref_step = run()
+    model.linear = packed_linear
+    assert oracle.rel_err(got_prefill, ref_prefill) <= 1e-2
+    assert oracle.rel_err(got_step, ref_step) <= 1e-2
+
+
 def _shard_worker(rank, world, port, out):
     import torch.distributed as dist
     from matgptq_b200 import decode

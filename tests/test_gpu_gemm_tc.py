@@ -110,3 +110,75 @@ def test_workspace_contract(lib, cuda):
                                     y_plain.data_ptr(), torch.cuda.current_stream().cuda_stream, flag,
                                     small.data_ptr(), 16, 2, 4)
     assert st == 1
+
+
+_LLAMA = {"q_o": (4096, 4096), "k_v": (4096, 1024), "gate_up": (4096, 14336), "down": (14336, 4096)}
+
+
+@pytest.mark.parametrize("b", [3, 4, 8])
+@pytest.mark.parametrize("shape", list(_LLAMA))
+def test_tensor_core_regime_grid_bf16(cuda, shape, b):
+    """Every cell of the tensor-core regime the benchmark times: the four Llama-3-8B shapes x M in
+    {32, 64, 128, 256} x b in {3, 4, 8}, bf16, through the operator (automatic path and K split), against the
+    oracle's dequantise-then-matmul.  For the two large layers the comparison runs on every seventh
+    out-feature (all 128-row tiles are hit) to bound the CPU time of the oracle."""
+    from matgptq_b200 import ops  # noqa: F401
+    n_in, n_out = _LLAMA[shape]
+    layer = synth.make_layer(n_out, n_in, 128, seed=300 + b, sym=True, dtype=torch.bfloat16, device=cuda)
+    packed, scales_r, flag = _pack(layer, n_out, n_in, 128, b, torch.bfloat16)
+    rows = torch.arange(0, n_out, 7 if n_out * n_in > 4096 * 4096 else 1)
+    w_ref = oracle.dequantize_weight(layer.qweight.cpu()[rows], layer.scales.cpu()[rows], layer.zeros.cpu()[rows], 8, b)
+    for m in (32, 64, 128, 256):
+        x = synth.make_activations(m, n_in, seed=m, dtype=torch.bfloat16, device=cuda)
+        y = torch.ops.matgptq_cuda.matmul_matgptq(x, packed, scales_r, n_out, n_in, b, 128, flag)
+        assert _status_ok()
+        y_ref = oracle.linear_fp32_accumulate(x.cpu(), w_ref)
+        assert oracle.rel_err(y.cpu()[:, rows], y_ref) <= TOL, f"M={m}"
+        assert oracle.elementwise_err(y.cpu()[:, rows], y_ref, rtol=1e-2, atol_rms=2e-2) <= 1.0, f"M={m}"
+
+
+@pytest.mark.parametrize("b", BITS)
+@pytest.mark.parametrize("gs", [-1, 32, 128])
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_dense_tile_is_bit_exact(cuda, b, gs, dtype):
+    """The weights the tensor-core path builds in shared memory, read back through the product itself: with
+    one-hot activation rows (row i = unit vector k0 + i) every output is a single weight times one, so
+    y[i, n] must equal dequantize()[n, k0 + i] bit for bit (fp32 accumulation of one term, exact rounding).
+    With one scale per row (gs == -1) the kernel scales the fp32 sum instead: still one rounding."""
+    from matgptq_b200 import ops
+    n_out, n_in, m = 256, 512, 256
+    layer = synth.make_layer(n_out, n_in, gs, seed=40 + b, sym=True, dtype=dtype, device=cuda)
+    packed, scales_r, flag = _pack(layer, n_out, n_in, gs, b, dtype)
+    w_ref = oracle.dequantize_weight(layer.qweight.cpu(), layer.scales.cpu(), layer.zeros.cpu(), 8, b)
+    for k0 in (0, 256):
+        x = torch.zeros(m, n_in, dtype=dtype, device=cuda)
+        x[torch.arange(m), k0 + torch.arange(m)] = 1.0
+        y = ops.matmul_matgptq_raw(x, packed, scales_r, n_out, n_in, b, gs, flag, path=2)
+        assert _status_ok()
+        assert torch.equal(y.cpu(), w_ref[:, k0:k0 + m].t().contiguous()), f"k0={k0}"
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_dense_tile_scale_edges_b2(cuda, dtype):
+    """b = 2 folds a factor two into the scale: scales whose double leaves the finite range must still give
+    dequantize()'s weights (inf for codes off the zero point, zero for the code on it), as must tiny,
+    negative, zero and infinite scales."""
+    from matgptq_b200 import ops
+    n_out, n_in, m, b = 128, 256, 256, 2
+    big = torch.finfo(dtype).max
+    edge = torch.tensor([big, -big, big / 2, big / 1.5, float("inf"), 0.0, -0.0, torch.finfo(dtype).tiny,
+                         torch.finfo(dtype).tiny / 4, -3.0, 1.0, 6e-5], dtype=torch.float32).to(dtype)
+    scales = edge[torch.arange(n_out * 2) % len(edge)].reshape(n_out, 2).contiguous()
+    g = torch.Generator().manual_seed(3)
+    q = torch.randint(0, 256, (n_out, n_in), dtype=torch.uint8, generator=g)
+    packed = torch.ops.matgptq_cuda.slice_pack_matgptq_qweights(q.to(cuda), n_out, n_in, 8, b, 128, 1 | (2 if dtype == torch.bfloat16 else 0))
+    scales_r = torch.ops.matgptq_cuda.reorder_matgptq_scales(scales.to(cuda), n_out, n_in, 128)
+    w_ref = oracle.dequantize_weight(q, scales, torch.full_like(scales, 128.0), 8, b)
+    x = torch.zeros(m, n_in, dtype=dtype, device=cuda)
+    x[torch.arange(m), torch.arange(m)] = 1.0
+    y = ops.matmul_matgptq_raw(x, packed, scales_r, n_out, n_in, b, 128, 1 | (2 if dtype == torch.bfloat16 else 0), path=2)
+    got, want = y.cpu().t().contiguous(), w_ref
+    # an infinite scale times the code on the zero point is NaN in dequantize() as well
+    assert torch.equal(torch.isnan(got), torch.isnan(want))
+    ok = ~torch.isnan(want)
+    assert torch.equal(got[ok], want[ok])

@@ -89,3 +89,25 @@ def test_pack_op_contract(cuda):
     fused = torch.ops.matgptq_cuda.slice_pack_matgptq_qweights(master, 32, 256, 8, 3, 128, 1)
     two = torch.ops.matgptq_cuda.pack_matgptq_qweights(oracle.matryoshka_slice(master, 8, 3), 32, 256, 3, 128, 1)
     assert torch.equal(fused, two)
+
+
+@pytest.mark.parametrize("code", [101, 102, 103])
+def test_a_wait_that_runs_out_is_reported_and_the_device_stays_usable(lib, cuda, code):
+    """Bounded waits: one warp waits on a barrier that nothing completes; the wait gives up, the status word
+    carries the code, reading it clears it, and kernels launched afterwards work."""
+    from matgptq_b200 import _native
+    assert _native.device_status() == 0
+    flag = torch.zeros(1, dtype=torch.int32, device=cuda)
+    st = lib.matgptq_b200_selftest_wait_timeout(code, flag.data_ptr(), torch.cuda.current_stream().cuda_stream)
+    assert st == 0
+    assert _native.device_status(reset=False) == code   # synchronises; the kernel has ended by itself
+    assert int(flag.item()) == 1
+    assert _native.device_status(reset=True) == code
+    assert _native.device_status() == 0
+    assert lib.matgptq_b200_selftest_wait_timeout(7, None, None) == 1  # not one of the wait codes
+    # the context is intact: a real launch right after
+    x = torch.arange(256, dtype=torch.uint8, device=cuda)
+    out = torch.empty_like(x)
+    assert lib.matgptq_b200_slice(x.data_ptr(), out.data_ptr(), 256, 8, 4, torch.cuda.current_stream().cuda_stream) == 0
+    torch.cuda.synchronize()
+    assert int(out.max()) == 15
