@@ -108,18 +108,26 @@ def decode_one_tokens(model, cur_token, input_pos, cache_position, past_key_valu
 class StaticCacheDecoder:
     """Prefill + token-by-token greedy decode over a ``StaticCache`` (``inference_demo_transformers.py:141-173``)."""
 
-    def __init__(self, model, compile_forward: bool = True):
+    def __init__(self, model, compile_forward: bool = True, backend: str = "inductor"):
+        """``backend="inductor"`` is the reference's setting (``mode="reduce-overhead"``: generated kernels
+        for the model's own elementwise work plus CUDA-graph replay).  ``backend="cudagraphs"`` traces the
+        same step with dynamo (fake tensors, so the operator's fake registration is exercised) and replays it
+        as a CUDA graph without generating code, for hosts whose C++ toolchain cannot build inductor's
+        wrappers."""
         self.model = model
         self.compile_forward = compile_forward
+        self.backend = backend
         self._decode = None
 
     def _decode_fn(self):
         if self._decode is None:
-            if self.compile_forward:
+            if not self.compile_forward:
+                self._decode = decode_one_tokens
+            elif self.backend == "inductor":
                 torch._dynamo.config.capture_scalar_outputs = True
                 self._decode = torch.compile(decode_one_tokens, fullgraph=True, dynamic=True, mode="reduce-overhead")
             else:
-                self._decode = decode_one_tokens
+                self._decode = torch.compile(decode_one_tokens, fullgraph=True, backend=self.backend)
         return self._decode
 
     @torch.no_grad()

@@ -160,25 +160,30 @@ def test_dense_tile_is_bit_exact(cuda, b, gs, dtype):
 
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
 def test_dense_tile_scale_edges_b2(cuda, dtype):
-    """b = 2 folds a factor two into the scale: scales whose double leaves the finite range must still give
-    dequantize()'s weights (inf for codes off the zero point, zero for the code on it), as must tiny,
-    negative, zero and infinite scales."""
+    """b = 2 folds a factor two into the scale.  A finite scale whose double leaves the finite range must
+    still give dequantize()'s weight for the code on the zero point: exactly zero (the doubled scale is
+    clamped to the largest finite value; an infinite one would turn 0 * scale into NaN).  Groups with such
+    scales hold only that code here, because any other code times such a scale is infinite in dequantize()
+    too and an infinite weight cannot be read back through a product.  Tiny, negative and zero scales ride
+    along with random codes."""
     from matgptq_b200 import ops
     n_out, n_in, m, b = 128, 256, 256, 2
+    flag = 1 | (2 if dtype == torch.bfloat16 else 0)
     big = torch.finfo(dtype).max
-    edge = torch.tensor([big, -big, big / 2, big / 1.5, float("inf"), 0.0, -0.0, torch.finfo(dtype).tiny,
-                         torch.finfo(dtype).tiny / 4, -3.0, 1.0, 6e-5], dtype=torch.float32).to(dtype)
+    tiny = torch.finfo(dtype).tiny
+    edge = torch.tensor([big, -big, big / 1.5, 0.0, -0.0, tiny, tiny / 4, -3.0, 1.0, 6e-5], dtype=torch.float32).to(dtype)
     scales = edge[torch.arange(n_out * 2) % len(edge)].reshape(n_out, 2).contiguous()
     g = torch.Generator().manual_seed(3)
     q = torch.randint(0, 256, (n_out, n_in), dtype=torch.uint8, generator=g)
-    packed = torch.ops.matgptq_cuda.slice_pack_matgptq_qweights(q.to(cuda), n_out, n_in, 8, b, 128, 1 | (2 if dtype == torch.bfloat16 else 0))
+    huge = (scales.float().abs() * 2 > big).repeat_interleave(128, dim=1)
+    assert huge.any() and not huge.all()
+    q[huge] = 128  # slices to code 2 = the implicit zero point of 2-bit codes
+    packed = torch.ops.matgptq_cuda.slice_pack_matgptq_qweights(q.to(cuda), n_out, n_in, 8, b, 128, flag)
     scales_r = torch.ops.matgptq_cuda.reorder_matgptq_scales(scales.to(cuda), n_out, n_in, 128)
     w_ref = oracle.dequantize_weight(q, scales, torch.full_like(scales, 128.0), 8, b)
+    assert torch.isfinite(w_ref.float()).all() and (w_ref[huge] == 0).all()
     x = torch.zeros(m, n_in, dtype=dtype, device=cuda)
     x[torch.arange(m), torch.arange(m)] = 1.0
-    y = ops.matmul_matgptq_raw(x, packed, scales_r, n_out, n_in, b, 128, 1 | (2 if dtype == torch.bfloat16 else 0), path=2)
-    got, want = y.cpu().t().contiguous(), w_ref
-    # an infinite scale times the code on the zero point is NaN in dequantize() as well
-    assert torch.equal(torch.isnan(got), torch.isnan(want))
-    ok = ~torch.isnan(want)
-    assert torch.equal(got[ok], want[ok])
+    y = ops.matmul_matgptq_raw(x, packed, scales_r, n_out, n_in, b, 128, flag, path=2)
+    assert _status_ok()
+    assert torch.equal(y.cpu().t().contiguous(), w_ref)
