@@ -94,6 +94,27 @@ int matgptq_b200_matmul_ws(int64_t bitwidth, int64_t group_size, int64_t n_out, 
                            const void *w, const void *s, const void *x, void *y, void *stream, uint32_t flags,
                            void *workspace, int64_t workspace_bytes, int path, int split_k);
 
+/*
+ * Grouped product: n_segments weight matrices over the SAME activations, y[M, sum N_i] = x[M,K] . [W_0; W_1; ...]^T,
+ * each segment with its own packed weights, scales, out-features N_i and bitwidth b_i (all with the same K and
+ * group size); segment i fills the columns [sum_{j<i} N_j, +N_i) of y.  This is the fused qkv / gate_up layer
+ * of a model whose checkpoint layers carry different bitwidths (vLLM fuses them into one layer,
+ * inference_lib/vllm_matgptq.py:113-121; the bitwidth file of evo_quant_search.py:659-671 gives each its own b).
+ * Batches below 32 run as ONE kernel launch (every CTA looks its segment up in a table); larger batches run the
+ * tensor-core path once per segment into the column block of that segment (workspace as for
+ * matgptq_b200_matmul_ws, sized for the largest segment; may be NULL).  Up to 8 segments.  The reference has no
+ * counterpart: its operator takes one bitwidth per call.
+ */
+typedef struct {
+  const void *w;    /* device, packed by matgptq_b200_pack_qweights at this segment's bitwidth */
+  const void *s;    /* device, reordered scales of this segment */
+  int64_t n_out;    /* out-features of this segment, a multiple of 16 */
+  int64_t bitwidth; /* 2, 3, 4, 6 or 8 */
+} matgptq_b200_segment;
+int matgptq_b200_matmul_grouped(const matgptq_b200_segment *segments, int n_segments, int64_t group_size, int64_t n_in,
+                                int64_t batch, const void *x, void *y, void *stream, uint32_t flags, void *workspace,
+                                int64_t workspace_bytes);
+
 /* Scratch bytes matgptq_b200_matmul_ws wants for this shape on the current device (0 = none). */
 int64_t matgptq_b200_matmul_workspace_bytes(int64_t n_out, int64_t n_in, int64_t batch);
 

@@ -22,6 +22,11 @@ _c_int = ctypes.c_int
 _c_u32 = ctypes.c_uint32
 _c_ptr = ctypes.c_void_p
 
+class Segment(ctypes.Structure):
+    """``matgptq_b200_segment`` of the C header: one weight matrix of a grouped product."""
+    _fields_ = [("w", ctypes.c_void_p), ("s", ctypes.c_void_p), ("n_out", ctypes.c_int64), ("bitwidth", ctypes.c_int64)]
+
+
 # symbol -> (restype, argtypes); must list every function declared in include/matgptq_b200.h
 SIGNATURES = {
     "matgptq_b200_version": (_c_int, []),
@@ -30,6 +35,7 @@ SIGNATURES = {
     "matgptq_b200_matmul_zp": (_c_int, [_c_i64, _c_i64, _c_i64, _c_i64, _c_i64, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_u32]),
     "matgptq_b200_matmul_tuned": (_c_int, [_c_i64, _c_i64, _c_i64, _c_i64, _c_i64, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_u32, _c_int, _c_int]),
     "matgptq_b200_matmul_ws": (_c_int, [_c_i64, _c_i64, _c_i64, _c_i64, _c_i64, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_u32, _c_ptr, _c_i64, _c_int, _c_int]),
+    "matgptq_b200_matmul_grouped": (_c_int, [ctypes.POINTER(Segment), _c_int, _c_i64, _c_i64, _c_i64, _c_ptr, _c_ptr, _c_ptr, _c_u32, _c_ptr, _c_i64]),
     "matgptq_b200_matmul_workspace_bytes": (_c_i64, [_c_i64, _c_i64, _c_i64]),
     "matgptq_b200_matmul_static_scratch": (_c_int, [_c_i64, _c_i64, _c_i64, _c_i64, _c_i64, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_u32]),
     "matgptq_b200_add_rmsnorm": (_c_int, [_c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_i64, _c_i64, ctypes.c_float, _c_u32, _c_ptr]),

@@ -118,6 +118,59 @@ int matgptq_b200_matmul_ws(int64_t bitwidth, int64_t group_size, int64_t n_out, 
                      0, split_k);
 }
 
+int matgptq_b200_matmul_grouped(const matgptq_b200_segment *segments, int n_segments, int64_t group_size, int64_t n_in,
+                                int64_t batch, const void *x, void *y, void *stream, uint32_t flags, void *workspace,
+                                int64_t workspace_bytes) {
+  if (!segments || n_segments < 1 || n_segments > 8 || workspace_bytes < 0) return MG_ERR_BAD_ARG;
+  int64_t total = 0;
+  for (int i = 0; i < n_segments; ++i) {
+    const int st = check_shape(segments[i].n_out, n_in, segments[i].bitwidth, group_size);
+    if (st != MG_OK) return st;
+    if (!segments[i].w || !segments[i].s) return MG_ERR_BAD_ARG;
+    if (!aligned16(segments[i].w) || !aligned16(segments[i].s)) return MG_ERR_ALIGNMENT;
+    total += segments[i].n_out;
+  }
+  if (batch < 0 || batch > (1 << 24) || total > (1 << 24)) return MG_ERR_BAD_ARG;
+  if (batch == 0) return MG_OK;
+  if (!x || !y) return MG_ERR_BAD_ARG;
+  if (!aligned16(x) || (reinterpret_cast<uintptr_t>(y) & 1u) || (workspace && !aligned16(workspace))) return MG_ERR_ALIGNMENT;
+  cudaStream_t cs = static_cast<cudaStream_t>(stream);
+  const bool bf16 = (flags & MATGPTQ_B200_FLAG_BF16) != 0;
+  const bool pdl = (flags & MATGPTQ_B200_FLAG_PDL) != 0;
+  int r = MG_ERR_UNSUPPORTED;
+  if (batch < kTensorCoreMinBatch) {
+    mg::GroupedSegment segs[8];
+    for (int i = 0; i < n_segments; ++i)
+      segs[i] = mg::GroupedSegment{segments[i].w, segments[i].s, static_cast<int>(segments[i].n_out),
+                                   static_cast<int>(segments[i].bitwidth)};
+    r = mg::gemv_grouped_launch(segs, n_segments, static_cast<int>(group_size), static_cast<int>(n_in),
+                                static_cast<int>(batch), x, y, static_cast<int>(total), bf16, pdl, cs);
+  }
+  if (r == MG_ERR_UNSUPPORTED) {
+    // one launch per segment into its column block: the tensor-core path, or segments that cannot share a launch shape
+    int64_t col = 0;
+    for (int i = 0; i < n_segments; ++i) {
+      unsigned char *yi = static_cast<unsigned char *>(y) + col * 2;
+      if (batch >= kTensorCoreMinBatch)
+        r = mg::gemm_tc_launch(static_cast<int>(segments[i].bitwidth), static_cast<int>(group_size),
+                               static_cast<int>(segments[i].n_out), static_cast<int>(n_in), static_cast<int>(batch),
+                               segments[i].w, segments[i].s, x, yi, workspace, workspace_bytes, bf16, pdl, 0, cs,
+                               static_cast<int>(total));
+      else
+        r = mg::gemv_launch(static_cast<int>(segments[i].bitwidth), static_cast<int>(group_size),
+                            static_cast<int>(segments[i].n_out), static_cast<int>(n_in), static_cast<int>(batch),
+                            segments[i].w, segments[i].s, nullptr, x, yi, bf16, pdl, 0, 0, cs, static_cast<int>(total));
+      if (r != MG_OK) return r;
+      col += segments[i].n_out;
+    }
+  }
+  if (r != MG_OK) return r;
+  if (!(flags & MATGPTQ_B200_FLAG_ASYNC)) {
+    if (cudaStreamSynchronize(cs) != cudaSuccess) return MG_ERR_CUDA;
+  }
+  return MG_OK;
+}
+
 int64_t matgptq_b200_matmul_workspace_bytes(int64_t n_out, int64_t n_in, int64_t batch) {
   if (n_out <= 0 || n_in <= 0 || batch <= 0) return 0;
   int sms = 0;

@@ -46,15 +46,12 @@ struct GemmParams {
   uint16_t *y;
   float *partial;  // [split][M][N] fp32 when split > 1
   int N, K, M;
+  int ldy;      // elements between two rows of y (N unless the call writes a column block of a wider output)
   int kblocks;  // K / 128
   int split;    // CTAs along K
   int ncols;    // UMMA N: batch rows per pass rounded up to 16
   int stages;
 };
-
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
 
 // TMA load of one box of a 2-D tensor map into shared memory; x (the innermost coordinate) times the element
 // size must be a multiple of 16 bytes: here x is a multiple of 64 two-byte elements.
@@ -354,9 +351,9 @@ __global__ void __launch_bounds__(kTcThreads, 2) gemm_tc_kernel(const GemmParams
             if (p.split > 1) {
               p.partial[(static_cast<size_t>(sk) * p.M + m) * p.N + n] = f;
             } else if (BF16) {
-              p.y[static_cast<size_t>(m) * p.N + n] = __bfloat16_as_ushort(__float2bfloat16_rn(f));
+              p.y[static_cast<size_t>(m) * p.ldy + n] = __bfloat16_as_ushort(__float2bfloat16_rn(f));
             } else {
-              p.y[static_cast<size_t>(m) * p.N + n] = __half_as_ushort(__float2half_rn(f));
+              p.y[static_cast<size_t>(m) * p.ldy + n] = __half_as_ushort(__float2half_rn(f));
             }
           }
         }
@@ -370,9 +367,10 @@ __global__ void __launch_bounds__(kTcThreads, 2) gemm_tc_kernel(const GemmParams
   }
 }
 
-// partial[split][M][N] fp32 -> y[M][N], added in a fixed order
+// partial[split][M][N] fp32 -> y[M][N] (rows ldy elements apart), added in a fixed order
 template <bool BF16>
-__global__ void splitk_reduce_kernel(const float *__restrict__ partial, uint16_t *__restrict__ y, long long mn, int split) {
+__global__ void splitk_reduce_kernel(const float *__restrict__ partial, uint16_t *__restrict__ y, long long mn, int split,
+                                     int n_cols, int ldy) {
   // launched with programmatic stream serialization right behind the kernel that writes `partial`
   asm volatile("griddepcontrol.launch_dependents;");
   asm volatile("griddepcontrol.wait;" ::: "memory");
@@ -380,7 +378,8 @@ __global__ void splitk_reduce_kernel(const float *__restrict__ partial, uint16_t
        i += static_cast<long long>(gridDim.x) * blockDim.x) {
     float sum = 0.f;
     for (int s = 0; s < split; ++s) sum += partial[static_cast<long long>(s) * mn + i];
-    y[i] = BF16 ? __bfloat16_as_ushort(__float2bfloat16_rn(sum)) : __half_as_ushort(__float2half_rn(sum));
+    const long long m = i / n_cols;
+    y[m * ldy + (i - m * n_cols)] = BF16 ? __bfloat16_as_ushort(__float2bfloat16_rn(sum)) : __half_as_ushort(__float2half_rn(sum));
   }
 }
 
@@ -483,7 +482,7 @@ static int launch_gemm_tc(GemmParams p, cudaStream_t stream, bool pdl) {
     rattr[0].val.programmaticStreamSerializationAllowed = 1;
     rcfg.attrs = rattr;
     rcfg.numAttrs = 1;
-    if (cudaLaunchKernelEx(&rcfg, splitk_reduce_kernel<BF16>, static_cast<const float *>(p.partial), p.y, mn, p.split) != cudaSuccess)
+    if (cudaLaunchKernelEx(&rcfg, splitk_reduce_kernel<BF16>, static_cast<const float *>(p.partial), p.y, mn, p.split, p.N, p.ldy) != cudaSuccess)
       return MG_ERR_CUDA;
   }
   return MG_OK;
@@ -508,7 +507,7 @@ static int launch_gemm_tc_group(const GemmParams &p, int group_size, bool bf16, 
 // workspace: fp32 scratch of at least gemm_tc_workspace_bytes(), or null to run without a K split
 int gemm_tc_launch(int bitwidth, int group_size, int N, int K, int M, const void *w, const void *s, const void *x,
                    void *y, void *workspace, long long workspace_bytes, bool bf16, bool pdl, int split_override,
-                   cudaStream_t stream) {
+                   cudaStream_t stream, int ldy) {
   int sm_count = 0;  // of the current device: the same value matgptq_b200_matmul_workspace_bytes sized the scratch with
   {
     const int st = current_device_sm_count(&sm_count);
@@ -523,6 +522,7 @@ int gemm_tc_launch(int bitwidth, int group_size, int N, int K, int M, const void
   p.N = N;
   p.K = K;
   p.M = M;
+  p.ldy = ldy > 0 ? ldy : N;
   p.kblocks = K / 128;
   int split = split_override > 0 ? split_override : gemm_tc_pick_split(N, K, M, sm_count);
   if (split > p.kblocks) split = p.kblocks;

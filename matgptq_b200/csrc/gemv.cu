@@ -57,6 +57,7 @@ struct GemvParams {
   const uint16_t *x;
   uint16_t *y;
   int N, K, M;
+  int ldy;      // elements between two rows of y (N unless the call writes a column block of a wider output)
   int tiles;    // N / 16
   int kblocks;  // K / 128
   int split;    // CTAs per cluster along K
@@ -102,8 +103,10 @@ __host__ __device__ inline SmemPlan make_plan(int R, int M, int max_nblk, int st
 
 // B: bitwidth, GS: group size (-1, 32, 128), BF16: activation/scale/output type,
 // NT: batch tiles of 8 rows handled per pass.
+// The whole computation of one CTA; `block_x` is the CTA's index among the CTAs of this product (blockIdx.x for a
+// plain launch, the index inside its segment for a grouped one).
 template <int B, int GS, bool BF16, int NT, bool ZP>
-__global__ void __launch_bounds__(512, 1) gemv_kernel(const GemvParams p) {
+__device__ __forceinline__ void gemv_body(const GemvParams &p, const int block_x) {
   extern __shared__ __align__(128) unsigned char smem_raw[];
 
   const int lane = threadIdx.x & 31;
@@ -113,7 +116,7 @@ __global__ void __launch_bounds__(512, 1) gemv_kernel(const GemvParams p) {
   const int S = p.split;
   const int crank = (S > 1) ? static_cast<int>(cg::this_cluster().block_rank()) : 0;
   const int log2s = 31 - __clz(S);  // S is a power of two (checked by the host)
-  const int rg = blockIdx.x >> log2s;
+  const int rg = block_x >> log2s;
   // The CTA's warps form Rt row tiles x RK slices of the CTA's K range.
   const int RK = p.kslices;
   const int Rt = R / RK;
@@ -505,7 +508,7 @@ __global__ void __launch_bounds__(512, 1) gemv_kernel(const GemvParams p) {
         for (int e = 0; e < 2; ++e) {
           const int m = nt * 8 + 2 * t + e;
           if (m < mvalid) {
-            uint16_t *dst = p.y + static_cast<size_t>(m0 + m) * p.N + n0 + tw * 16 + g;
+            uint16_t *dst = p.y + static_cast<size_t>(m0 + m) * p.ldy + n0 + tw * 16 + g;
             dst[0] = float_to_out<BF16>(yacc[nt][e] * mlo);
             dst[8] = float_to_out<BF16>(yacc[nt][2 + e] * mhi);
           }
@@ -553,10 +556,75 @@ __global__ void __launch_bounds__(512, 1) gemv_kernel(const GemvParams p) {
       const int m = static_cast<int>((static_cast<float>(idx) + 0.5f) * inv_cw), j = idx - m * cw;
       float sum = 0.f;
       for (int r = 0; r < nslots; ++r) sum += red[(r * plan.xrows + m) * cw + j];
-      if (nbase + j < p.N) p.y[static_cast<size_t>(m0 + m) * p.N + nbase + j] = float_to_out<BF16>(sum);
+      if (nbase + j < p.N) p.y[static_cast<size_t>(m0 + m) * p.ldy + nbase + j] = float_to_out<BF16>(sum);
     }
   }
 }
+
+template <int B, int GS, bool BF16, int NT, bool ZP>
+__global__ void __launch_bounds__(512, 1) gemv_kernel(const GemvParams p) {
+  gemv_body<B, GS, BF16, NT, ZP>(p, static_cast<int>(blockIdx.x));
+}
+
+#if !MG_GEMV_ZP
+// ----------------------------------------------------------------------------
+// Grouped launch: several products over the SAME activations in one kernel, each with its own packed
+// weights, scales, out-features and bitwidth, written side by side into one output [M, sum N_i].  This is
+// what a fused qkv or gate_up layer with per-layer bitwidths needs (vLLM fuses those layers,
+// inference_lib/vllm_matgptq.py:113-121; a bitwidth file gives each checkpoint layer its own b,
+// evo_quant_search.py:659-671): one launch and one fixed cost instead of one per bitwidth segment.
+// Every CTA finds its segment from the table and runs that segment's body; all segments share the launch
+// shape (warps, K slices, cluster size) and the shared-memory request.
+// ----------------------------------------------------------------------------
+constexpr int kMaxSegments = 8;
+
+struct GroupedParams {
+  const uint32_t *w[kMaxSegments];
+  const uint16_t *s[kMaxSegments];
+  int n_out[kMaxSegments];
+  int col0[kMaxSegments];    // first output column of the segment
+  int cta0[kMaxSegments + 1];  // first CTA (blockIdx.x) of the segment; cta0[nseg] = gridDim.x
+  signed char bits[kMaxSegments];
+  signed char stages[kMaxSegments];
+  int nseg;
+  const uint16_t *x;
+  uint16_t *y;
+  int ldy, K, M, kblocks, split, xblocks, kslices;
+};
+
+template <int GS, bool BF16, int NT>
+__global__ void __launch_bounds__(512, 1) gemv_grouped_kernel(const GroupedParams gp) {
+  int seg = 0;
+  const int bx = static_cast<int>(blockIdx.x);
+#pragma unroll
+  for (int i = 1; i < kMaxSegments; ++i)
+    if (i < gp.nseg && bx >= gp.cta0[i]) seg = i;
+  GemvParams p;
+  p.w = gp.w[seg];
+  p.s = gp.s[seg];
+  p.z = nullptr;
+  p.x = gp.x;
+  p.y = gp.y + gp.col0[seg];
+  p.N = gp.n_out[seg];
+  p.K = gp.K;
+  p.M = gp.M;
+  p.ldy = gp.ldy;
+  p.tiles = p.N / 16;
+  p.kblocks = gp.kblocks;
+  p.split = gp.split;
+  p.stages = gp.stages[seg];
+  p.xblocks = gp.xblocks;
+  p.kslices = gp.kslices;
+  const int local = bx - gp.cta0[seg];
+  switch (gp.bits[seg]) {  // uniform over the CTA (and over its cluster: segments start at cluster boundaries)
+    case 2: gemv_body<2, GS, BF16, NT, false>(p, local); break;
+    case 3: gemv_body<3, GS, BF16, NT, false>(p, local); break;
+    case 4: gemv_body<4, GS, BF16, NT, false>(p, local); break;
+    case 6: gemv_body<6, GS, BF16, NT, false>(p, local); break;
+    default: gemv_body<8, GS, BF16, NT, false>(p, local); break;
+  }
+}
+#endif
 
 // ----------------------------------------------------------------------------
 // host side
@@ -703,7 +771,8 @@ static int launch_shape(GemvParams p, const GemvShape &c, int bitwidth, int grou
 
 // z: zero points (reordered like the scales) for the build with zero points, null for the other one
 int MG_GEMV_LAUNCH(int bitwidth, int group_size, int N, int K, int M, const void *w, const void *s, const void *z,
-                   const void *x, void *y, bool bf16, bool pdl, int R_override, int S_override, cudaStream_t stream) {
+                   const void *x, void *y, bool bf16, bool pdl, int R_override, int S_override, cudaStream_t stream,
+                   int ldy) {
   if (kZP != (z != nullptr)) return MG_ERR_BAD_ARG;
   int sm_count = 0;
   {
@@ -719,6 +788,7 @@ int MG_GEMV_LAUNCH(int bitwidth, int group_size, int N, int K, int M, const void
   p.N = N;
   p.K = K;
   p.M = M;
+  p.ldy = ldy > 0 ? ldy : N;
   p.tiles = N / 16;
   p.kblocks = K / 128;
   GemvShape first, second;
@@ -739,6 +809,138 @@ int MG_GEMV_LAUNCH(int bitwidth, int group_size, int N, int K, int M, const void
   if (r == MG_ERR_UNSUPPORTED) r = launch_shape(p, second, bitwidth, group_size, bf16, pdl, stream);
   return r;
 }
+
+#if !MG_GEMV_ZP
+// ---- grouped launch, host side --------------------------------------------------------------------------
+template <int GS, int NT> static SmemPlan plan_for_bits(int bits, int R, int M, int max_nblk, int stages, int xblocks) {
+  switch (bits) {
+    case 2: return make_plan<2, GS, NT, false>(R, M, max_nblk, stages, xblocks);
+    case 3: return make_plan<3, GS, NT, false>(R, M, max_nblk, stages, xblocks);
+    case 4: return make_plan<4, GS, NT, false>(R, M, max_nblk, stages, xblocks);
+    case 6: return make_plan<6, GS, NT, false>(R, M, max_nblk, stages, xblocks);
+    default: return make_plan<8, GS, NT, false>(R, M, max_nblk, stages, xblocks);
+  }
+}
+
+template <int GS, bool BF16, int NT>
+static int launch_grouped(GroupedParams gp, const GroupedSegment *segments, const GemvShape &c, cudaStream_t stream, bool pdl) {
+  auto kernel = gemv_grouped_kernel<GS, BF16, NT>;
+  const int R = c.R, S = c.S, RK = c.RK;
+  if (R < 1 || R > 16 || S < 1 || S > 8 || (S & (S - 1)) != 0 || S > gp.kblocks) return MG_ERR_UNSUPPORTED;
+  if (RK < 1 || R % RK != 0 || RK > gp.kblocks / S) return MG_ERR_UNSUPPORTED;
+  const int Rt = R / RK;
+  if (Rt * 16 % S != 0) return MG_ERR_UNSUPPORTED;
+  const int max_nblk = (gp.kblocks + S - 1) / S;
+  const int ctas_per_sm = R >= 16 ? 1 : 16 / R;
+  const int budget = smem_for_ctas_per_sm(ctas_per_sm);
+  // activations: the CTA's whole K slice when that leaves every segment two ring stages, else stages of a few blocks
+  int xblocks = max_nblk;
+  for (int i = 0; i < gp.nseg; ++i)
+    if (plan_for_bits<GS, NT>(gp.bits[i], R, gp.M, max_nblk, 2, xblocks).total > budget) xblocks = 0;
+  if (xblocks == 0) {
+    if (RK > 1) return MG_ERR_UNSUPPORTED;
+    xblocks = (NT == 1) ? 8 : 4;
+    if (xblocks > max_nblk) xblocks = max_nblk;
+  }
+  int smem = smem_for_ctas_per_sm(ctas_per_sm + 1) + 1;  // padded so that one CTA more does not fit on the SM
+  int cta = 0;
+  for (int i = 0; i < gp.nseg; ++i) {
+    const int cb = gp.bits[i] <= 4 ? 4 : 2;  // ChunkBlocks
+    const int nchunks = (max_nblk + cb - 1) / cb;
+    int stages = 2;
+    while (stages < 8 && stages < nchunks &&
+           plan_for_bits<GS, NT>(gp.bits[i], R, gp.M, max_nblk, stages + 1, xblocks).total <= budget)
+      ++stages;
+    const int total = plan_for_bits<GS, NT>(gp.bits[i], R, gp.M, max_nblk, stages, xblocks).total;
+    if (total > 227 * 1024 - 1024) return MG_ERR_UNSUPPORTED;
+    if (total > smem) smem = total;
+    gp.stages[i] = static_cast<signed char>(stages);
+    gp.cta0[i] = cta;
+    cta += ((segments[i].n_out / 16 + Rt - 1) / Rt) * S;
+  }
+  gp.cta0[gp.nseg] = cta;
+  gp.split = S;
+  gp.kslices = RK;
+  gp.xblocks = xblocks;
+  if (smem > 48 * 1024) {
+    static SharedMemoryOptIn opt_in;
+    const int st = opt_in.ensure(kernel, 226 * 1024);
+    if (st != MG_OK) return st;
+  }
+  const int passes = (gp.M + NT * 8 - 1) / (NT * 8);
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(cta, passes, 1);
+  cfg.blockDim = dim3(R * 32, 1, 1);
+  cfg.dynamicSmemBytes = static_cast<size_t>(smem);
+  cfg.stream = stream;
+  cudaLaunchAttribute attrs[2];
+  int na = 0;
+  if (S > 1) {
+    attrs[na].id = cudaLaunchAttributeClusterDimension;
+    attrs[na].val.clusterDim.x = S;
+    attrs[na].val.clusterDim.y = 1;
+    attrs[na].val.clusterDim.z = 1;
+    ++na;
+  }
+  if (pdl) {
+    attrs[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attrs[na].val.programmaticStreamSerializationAllowed = 1;
+    ++na;
+  }
+  cfg.attrs = attrs;
+  cfg.numAttrs = na;
+  return cudaLaunchKernelEx(&cfg, kernel, gp) == cudaSuccess ? MG_OK : MG_ERR_CUDA;
+}
+
+template <int GS>
+static int launch_grouped_gs(const GroupedParams &gp, const GroupedSegment *segments, const GemvShape &c, bool bf16,
+                             cudaStream_t stream, bool pdl) {
+  if (gp.M <= 8)
+    return bf16 ? launch_grouped<GS, true, 1>(gp, segments, c, stream, pdl) : launch_grouped<GS, false, 1>(gp, segments, c, stream, pdl);
+  return bf16 ? launch_grouped<GS, true, 2>(gp, segments, c, stream, pdl) : launch_grouped<GS, false, 2>(gp, segments, c, stream, pdl);
+}
+
+int gemv_grouped_launch(const GroupedSegment *segments, int nseg, int group_size, int K, int M, const void *x, void *y,
+                        int ldy, bool bf16, bool pdl, cudaStream_t stream) {
+  if (nseg < 1 || nseg > kMaxSegments) return MG_ERR_UNSUPPORTED;
+  int sm_count = 0;
+  {
+    const int st = current_device_sm_count(&sm_count);
+    if (st != MG_OK) return st;
+  }
+  GroupedParams gp = {};
+  int tiles = 0, col = 0;
+  for (int i = 0; i < nseg; ++i) {
+    gp.w[i] = static_cast<const uint32_t *>(segments[i].w);
+    gp.s[i] = static_cast<const uint16_t *>(segments[i].s);
+    gp.n_out[i] = segments[i].n_out;
+    gp.col0[i] = col;
+    gp.bits[i] = static_cast<signed char>(segments[i].bitwidth);
+    col += segments[i].n_out;
+    tiles += segments[i].n_out / 16;
+  }
+  gp.nseg = nseg;
+  gp.x = static_cast<const uint16_t *>(x);
+  gp.y = static_cast<uint16_t *>(y);
+  gp.ldy = ldy;
+  gp.K = K;
+  gp.M = M;
+  gp.kblocks = K / 128;
+  GemvShape first, second;
+  gemv_pick_config(tiles, gp.kblocks, M < 16 ? M : 16, sm_count, &first, &second);
+  auto launch = [&](const GemvShape &c) {
+    switch (group_size) {
+      case -1: return launch_grouped_gs<-1>(gp, segments, c, bf16, stream, pdl);
+      case 32: return launch_grouped_gs<32>(gp, segments, c, bf16, stream, pdl);
+      case 128: return launch_grouped_gs<128>(gp, segments, c, bf16, stream, pdl);
+      default: return static_cast<int>(MG_ERR_BAD_ARG);
+    }
+  };
+  int r = launch(first);
+  if (r == MG_ERR_UNSUPPORTED) r = launch(second);
+  return r;
+}
+#endif
 
 MG_DEFINE_STATUS_ACCESSOR(MG_GEMV_STATUS)
 

@@ -16,9 +16,22 @@ namespace mg {
 // gemv.cu
 // z must be null for gemv_launch and non-null for gemv_zp_launch (gemv_zp.cu: the same kernels with zero points)
 int gemv_launch(int bitwidth, int group_size, int N, int K, int M, const void *w, const void *s, const void *z,
-                const void *x, void *y, bool bf16, bool pdl, int R_override, int S_override, cudaStream_t stream);
+                const void *x, void *y, bool bf16, bool pdl, int R_override, int S_override, cudaStream_t stream,
+                int ldy = 0);
 int gemv_zp_launch(int bitwidth, int group_size, int N, int K, int M, const void *w, const void *s, const void *z,
-                   const void *x, void *y, bool bf16, bool pdl, int R_override, int S_override, cudaStream_t stream);
+                   const void *x, void *y, bool bf16, bool pdl, int R_override, int S_override, cudaStream_t stream,
+                   int ldy = 0);
+
+// Grouped launch (gemv.cu): nseg products over the same activations, outputs side by side in y[M, ldy].
+// MG_ERR_UNSUPPORTED (nothing launched) when the segments cannot share one launch shape.
+struct GroupedSegment {
+  const void *w;
+  const void *s;
+  int n_out;
+  int bitwidth;
+};
+int gemv_grouped_launch(const GroupedSegment *segments, int nseg, int group_size, int K, int M, const void *x, void *y,
+                        int ldy, bool bf16, bool pdl, cudaStream_t stream);
 
 int gemv_device_status(int *status_out, int reset);
 int gemv_zp_device_status(int *status_out, int reset);
@@ -28,7 +41,7 @@ int gemm_tc_pick_split(int N, int K, int M, int sm_count);
 long long gemm_tc_workspace_bytes(int N, int K, int M, int sm_count);
 int gemm_tc_launch(int bitwidth, int group_size, int N, int K, int M, const void *w, const void *s, const void *x,
                    void *y, void *workspace, long long workspace_bytes, bool bf16, bool pdl, int split_override,
-                   cudaStream_t stream);
+                   cudaStream_t stream, int ldy = 0);
 int gemm_tc_device_status(int *status_out, int reset);
 
 // selftest.cu

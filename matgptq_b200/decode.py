@@ -87,17 +87,15 @@ class PackedLinear:
 
     def __call__(self, x: torch.Tensor, pdl: bool = False) -> torch.Tensor:
         flag = self.flag | (_native.FLAG_PDL if pdl else 0)
+        if len(self.parts) == 1:
+            rows, bits, packed, scales = self.parts[0]
+            return ops.matmul_matgptq_raw(x, packed, scales, rows, self.n_in, bits, self.group_size, flag)
+        # segments of different bitwidths: ONE grouped launch writes them side by side
         # (running the segments on parallel streams was measured: 419 tok/s against 446 at batch 1; the fork
         # and join events cost more than the overlap gives, and the launches lose their programmatic chaining)
-        if x.shape[0] == 1 and len(self.parts) > 1:  # one row: every segment writes its slice of the result in place
-            out, col = torch.empty(1, self.n_out, dtype=x.dtype, device=x.device), 0
-            for rows, bits, packed, scales in self.parts:
-                ops.matmul_matgptq_raw(x, packed, scales, rows, self.n_in, bits, self.group_size, flag, out=out[:, col:col + rows])
-                col += rows
-            return out
-        outs = [ops.matmul_matgptq_raw(x, packed, scales, rows, self.n_in, bits, self.group_size, flag)
-                for rows, bits, packed, scales in self.parts]
-        return outs[0] if len(outs) == 1 else torch.cat(outs, dim=-1)
+        return ops.matmul_matgptq_grouped_raw(x, [p[2] for p in self.parts], [p[3] for p in self.parts],
+                                              [p[0] for p in self.parts], self.n_in, [p[1] for p in self.parts],
+                                              self.group_size, flag)
 
     def weight_bytes(self) -> int:
         return sum(p.numel() * 4 + s.numel() * 2 for _, _, p, s in self.parts)

@@ -219,6 +219,78 @@ def _matmul_fake(input, matgptq_weights, matgptq_scales, n_out_features, n_in_fe
                            dtype=torch.bfloat16 if feature_flag & 2 else torch.float16)
 
 
+def matmul_matgptq_grouped_raw(x: torch.Tensor, packed, scales, n_out, n_in: int, bitwidths, group_size: int,
+                               flags: int, out: torch.Tensor | None = None,
+                               workspace: torch.Tensor | None = None) -> torch.Tensor:
+    """The C-ABI grouped product without checks: segment ``i`` (``packed[i]``, ``scales[i]``, ``n_out[i]`` rows at
+    ``bitwidths[i]`` bits) fills its column block of ``out [M, sum(n_out)]``.  One kernel launch below 32 rows."""
+    batch = x.size(-2)
+    total = int(sum(n_out))
+    if out is None:
+        out = torch.empty((batch, total), dtype=x.dtype, device=x.device)
+    segs = (_native.Segment * len(packed))()
+    need = 0
+    for i, (w, s, n, b) in enumerate(zip(packed, scales, n_out, bitwidths)):
+        segs[i] = _native.Segment(w.data_ptr(), s.data_ptr(), int(n), int(b))
+        if batch >= 32 and workspace is None:
+            need = max(need, _lib.matgptq_b200_matmul_workspace_bytes(int(n), n_in, batch))
+    if need > 0:
+        workspace = torch.empty(need, dtype=torch.uint8, device=x.device)
+    st = _lib.matgptq_b200_matmul_grouped(segs, len(packed), group_size, n_in, batch, x.data_ptr(), out.data_ptr(),
+                                          torch.cuda.current_stream(x.device).cuda_stream, flags,
+                                          workspace.data_ptr() if workspace is not None else None,
+                                          workspace.numel() if workspace is not None else 0)
+    _native.check(st, "matgptq_b200_matmul_grouped")
+    return out
+
+
+@torch.library.custom_op("matgptq_cuda::matmul_matgptq_grouped", mutates_args=())
+def matmul_matgptq_grouped(
+    input: torch.Tensor,
+    matgptq_weights: list[torch.Tensor],
+    matgptq_scales: list[torch.Tensor],
+    n_out_features: list[int],
+    n_in_features: int,
+    bitwidths: list[int],
+    group_size: int,
+    feature_flag: int,
+) -> torch.Tensor:
+    """Addition: ``matmul_matgptq`` for a fused layer whose output partitions have their own bitwidths
+    (``vllm_matgptq.py:113-121`` fuses q/k/v and gate/up; ``evo_quant_search.py:659-671`` gives each checkpoint
+    layer its own bitwidth).  ``y[M, sum N_i] = x[M, K] @ cat(Wdq_i).T`` in one launch for fewer than 32 rows;
+    the reference's operator takes a single bitwidth per call."""
+    if not (len(matgptq_weights) == len(matgptq_scales) == len(n_out_features) == len(bitwidths)) or not matgptq_weights:
+        raise RuntimeError("matmul_matgptq_grouped: one weight, scale, n_out_features and bitwidth per segment")
+    if len(matgptq_weights) > 8:
+        raise RuntimeError("matmul_matgptq_grouped: at most 8 segments")
+    bf16 = bool(feature_flag & _native.FLAG_BF16)
+    dtype = torch.bfloat16 if bf16 else torch.float16
+    for w, s, n, b in zip(matgptq_weights, matgptq_scales, n_out_features, bitwidths):
+        _check_matmul_args(input, w, s, n, n_in_features, b, group_size)
+        if s.dtype != dtype:
+            raise RuntimeError(f"matgptq_scales must be {dtype} for feature_flag={feature_flag}")
+    if input.dtype != dtype:
+        raise RuntimeError(f"input must be {dtype} for feature_flag={feature_flag}")
+    batch = input.size(-2)
+    x = input
+    if input.dim() > 2:
+        x = input.reshape(-1, batch, n_in_features)[0]
+    if not x.is_contiguous():
+        x = x.contiguous()
+    if x.data_ptr() % 16 != 0:
+        x = x.clone()
+    with torch.cuda.device(x.device):
+        return matmul_matgptq_grouped_raw(x, matgptq_weights, matgptq_scales, n_out_features, n_in_features, bitwidths,
+                                          group_size, feature_flag)
+
+
+@matmul_matgptq_grouped.register_fake
+def _matmul_grouped_fake(input, matgptq_weights, matgptq_scales, n_out_features, n_in_features, bitwidths, group_size,
+                         feature_flag):
+    return input.new_empty((input.shape[-2], sum(n_out_features)),
+                           dtype=torch.bfloat16 if feature_flag & 2 else torch.float16)
+
+
 @torch.library.custom_op("matgptq_cuda::matmul_matgptq_zeros", mutates_args=())
 def matmul_matgptq_zeros(
     input: torch.Tensor,

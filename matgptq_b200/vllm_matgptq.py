@@ -182,11 +182,15 @@ class MatGPTQLinearMethod(LinearMethodBase):
                 for (rows, bits), w, s, z in zip(layer.matgptq_segments, layer.matgptq_weights, layer.matgptq_scales,
                                                  layer.matgptq_zeros)
             ]
+        elif len(layer.matgptq_segments) == 1:
+            (rows, bits), = layer.matgptq_segments
+            outs = [torch.ops.matgptq_cuda.matmul_matgptq(x2, layer.matgptq_weights[0], layer.matgptq_scales[0], rows,
+                                                          layer.matgptq_n_in, bits, cfg.group_size, cfg.flag)]
         else:
-            outs = [
-                torch.ops.matgptq_cuda.matmul_matgptq(x2, w, s, rows, layer.matgptq_n_in, bits, cfg.group_size, cfg.flag)
-                for (rows, bits), w, s in zip(layer.matgptq_segments, layer.matgptq_weights, layer.matgptq_scales)
-            ]
+            # a fused layer whose partitions carry different bitwidths: one grouped launch, outputs side by side
+            outs = [torch.ops.matgptq_cuda.matmul_matgptq_grouped(
+                x2, list(layer.matgptq_weights), list(layer.matgptq_scales), [rows for rows, _ in layer.matgptq_segments],
+                layer.matgptq_n_in, [bits for _, bits in layer.matgptq_segments], cfg.group_size, cfg.flag)]
         y = outs[0] if len(outs) == 1 else torch.cat(outs, dim=-1)
         y = y.view(*x.shape[:-1], y.shape[-1])
         if bias is not None:
