@@ -110,10 +110,10 @@ class StaticCacheDecoder:
 
     def __init__(self, model, compile_forward: bool = True, backend: str = "inductor"):
         """``backend="inductor"`` is the reference's setting (``mode="reduce-overhead"``: generated kernels
-        for the model's own elementwise work plus CUDA-graph replay).  ``backend="cudagraphs"`` traces the
-        same step with dynamo (fake tensors, so the operator's fake registration is exercised) and replays it
-        as a CUDA graph without generating code, for hosts whose C++ toolchain cannot build inductor's
-        wrappers."""
+        for the model's own elementwise work plus CUDA-graph replay).  Any other dynamo backend name traces
+        the same step as one full graph (fake tensors, so the operator's fake registration is exercised)
+        without inductor; ``"eager"`` then runs the traced graph with the ordinary kernels, for hosts whose
+        C++ toolchain cannot build inductor's host code."""
         self.model = model
         self.compile_forward = compile_forward
         self.backend = backend
