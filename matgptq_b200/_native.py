@@ -27,6 +27,12 @@ class Segment(ctypes.Structure):
     _fields_ = [("w", ctypes.c_void_p), ("s", ctypes.c_void_p), ("n_out", ctypes.c_int64), ("bitwidth", ctypes.c_int64)]
 
 
+class Comm(ctypes.Structure):
+    """``matgptq_b200_comm`` of the C header: peer buffers of the fused row-parallel product + all-reduce."""
+    _fields_ = [("data", ctypes.c_void_p * 8), ("flags", ctypes.c_void_p * 8), ("ctrl", ctypes.c_void_p),
+                ("slot_elems", ctypes.c_int64), ("rank", ctypes.c_int), ("nranks", ctypes.c_int), ("push_only", ctypes.c_int)]
+
+
 # symbol -> (restype, argtypes); must list every function declared in include/matgptq_b200.h
 SIGNATURES = {
     "matgptq_b200_version": (_c_int, []),
@@ -36,6 +42,8 @@ SIGNATURES = {
     "matgptq_b200_matmul_tuned": (_c_int, [_c_i64, _c_i64, _c_i64, _c_i64, _c_i64, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_u32, _c_int, _c_int]),
     "matgptq_b200_matmul_ws": (_c_int, [_c_i64, _c_i64, _c_i64, _c_i64, _c_i64, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_u32, _c_ptr, _c_i64, _c_int, _c_int]),
     "matgptq_b200_matmul_grouped": (_c_int, [ctypes.POINTER(Segment), _c_int, _c_i64, _c_i64, _c_i64, _c_ptr, _c_ptr, _c_ptr, _c_u32, _c_ptr, _c_i64]),
+    "matgptq_b200_matmul_allreduce": (_c_int, [_c_i64, _c_i64, _c_i64, _c_i64, _c_i64, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_u32, ctypes.POINTER(Comm)]),
+    "matgptq_b200_allreduce_finish": (_c_int, [ctypes.POINTER(Comm), _c_ptr, _c_i64, _c_i64, _c_ptr, _c_u32]),
     "matgptq_b200_matmul_workspace_bytes": (_c_i64, [_c_i64, _c_i64, _c_i64]),
     "matgptq_b200_matmul_static_scratch": (_c_int, [_c_i64, _c_i64, _c_i64, _c_i64, _c_i64, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_u32]),
     "matgptq_b200_add_rmsnorm": (_c_int, [_c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_i64, _c_i64, ctypes.c_float, _c_u32, _c_ptr]),

@@ -171,6 +171,57 @@ int matgptq_b200_matmul_grouped(const matgptq_b200_segment *segments, int n_segm
   return MG_OK;
 }
 
+static int to_ar_params(const matgptq_b200_comm *comm, mg::ArParams *ar) {
+  if (!comm || comm->nranks < 1 || comm->nranks > mg::kArMaxRanks || comm->rank < 0 || comm->rank >= comm->nranks ||
+      !comm->ctrl || comm->slot_elems <= 0)
+    return MG_ERR_BAD_ARG;
+  for (int q = 0; q < comm->nranks; ++q) {
+    if (!comm->data[q] || !comm->flags[q]) return MG_ERR_BAD_ARG;
+    ar->data[q] = static_cast<float *>(comm->data[q]);
+    ar->flags[q] = static_cast<unsigned *>(comm->flags[q]);
+  }
+  ar->ctrl = static_cast<unsigned *>(comm->ctrl);
+  ar->slot_elems = comm->slot_elems;
+  ar->rank = comm->rank;
+  ar->nranks = comm->nranks;
+  ar->push_only = comm->push_only ? 1 : 0;
+  return MG_OK;
+}
+
+int matgptq_b200_matmul_allreduce(int64_t bitwidth, int64_t group_size, int64_t n_out, int64_t n_in_shard, int64_t batch,
+                                  const void *w, const void *s, const void *x, void *y, void *stream, uint32_t flags,
+                                  const matgptq_b200_comm *comm) {
+  const int st = check_shape(n_out, n_in_shard, bitwidth, group_size);
+  if (st != MG_OK) return st;
+  mg::ArParams ar = {};
+  const int sc = to_ar_params(comm, &ar);
+  if (sc != MG_OK) return sc;
+  if (batch <= 0 || batch > (1 << 24) || !w || !s || !x || !y) return MG_ERR_BAD_ARG;
+  if (!aligned16(w) || !aligned16(x) || !aligned16(s) || (reinterpret_cast<uintptr_t>(y) & 1u)) return MG_ERR_ALIGNMENT;
+  if (batch >= kTensorCoreMinBatch) return MG_ERR_UNSUPPORTED;
+  cudaStream_t cs = static_cast<cudaStream_t>(stream);
+  const int r = mg::gemv_allreduce_launch(static_cast<int>(bitwidth), static_cast<int>(group_size), static_cast<int>(n_out),
+                                          static_cast<int>(n_in_shard), static_cast<int>(batch), w, s, x, y,
+                                          (flags & MATGPTQ_B200_FLAG_BF16) != 0, (flags & MATGPTQ_B200_FLAG_PDL) != 0, ar, cs);
+  if (r != MG_OK) return r;
+  if (!(flags & MATGPTQ_B200_FLAG_ASYNC) && cudaStreamSynchronize(cs) != cudaSuccess) return MG_ERR_CUDA;
+  return MG_OK;
+}
+
+int matgptq_b200_allreduce_finish(const matgptq_b200_comm *comm, void *y, int64_t n_out, int64_t batch, void *stream,
+                                  uint32_t flags) {
+  mg::ArParams ar = {};
+  const int sc = to_ar_params(comm, &ar);
+  if (sc != MG_OK) return sc;
+  if (!y || n_out <= 0 || batch <= 0 || batch * n_out > comm->slot_elems) return MG_ERR_BAD_ARG;
+  cudaStream_t cs = static_cast<cudaStream_t>(stream);
+  const int r = mg::allreduce_finish_launch(ar, y, static_cast<int>(n_out), static_cast<int>(batch),
+                                            (flags & MATGPTQ_B200_FLAG_BF16) != 0, cs);
+  if (r != MG_OK) return r;
+  if (!(flags & MATGPTQ_B200_FLAG_ASYNC) && cudaStreamSynchronize(cs) != cudaSuccess) return MG_ERR_CUDA;
+  return MG_OK;
+}
+
 int64_t matgptq_b200_matmul_workspace_bytes(int64_t n_out, int64_t n_in, int64_t batch) {
   if (n_out <= 0 || n_in <= 0 || batch <= 0) return 0;
   int sms = 0;

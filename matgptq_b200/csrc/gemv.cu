@@ -105,8 +105,17 @@ __host__ __device__ inline SmemPlan make_plan(int R, int M, int max_nblk, int st
 // NT: batch tiles of 8 rows handled per pass.
 // The whole computation of one CTA; `block_x` is the CTA's index among the CTAs of this product (blockIdx.x for a
 // plain launch, the index inside its segment for a grouped one).
-template <int B, int GS, bool BF16, int NT, bool ZP>
-__device__ __forceinline__ void gemv_body(const GemvParams &p, const int block_x) {
+__device__ __forceinline__ void st_release_sys(unsigned *ptr, unsigned v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(ptr), "r"(v) : "memory");
+}
+__device__ __forceinline__ unsigned ld_acquire_sys(const unsigned *ptr) {
+  unsigned v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(ptr) : "memory");
+  return v;
+}
+
+template <int B, int GS, bool BF16, int NT, bool ZP, bool AR = false>
+__device__ __forceinline__ void gemv_body(const GemvParams &p, const int block_x, const ArParams *ar = nullptr) {
   extern __shared__ __align__(128) unsigned char smem_raw[];
 
   const int lane = threadIdx.x & 31;
@@ -499,7 +508,7 @@ __device__ __forceinline__ void gemv_body(const GemvParams &p, const int block_x
   const int cols = Rt * 16;
   const int n0 = rg * cols;
   const int nslots = S * RK;  // partial sums per output
-  if (nslots == 1) {
+  if (nslots == 1 && !AR) {
     // nothing to add up: lane (g, t) holds rows g, g+8 of its tile for the batch columns 2t, 2t+1 of every batch tile
     if (active) {
 #pragma unroll
@@ -552,11 +561,75 @@ __device__ __forceinline__ void gemv_body(const GemvParams &p, const int block_x
       __syncthreads();
     }
     const int nbase = n0 + crank * cw;
-    for (int idx = threadIdx.x; idx < mvalid * cw; idx += blockDim.x) {
-      const int m = static_cast<int>((static_cast<float>(idx) + 0.5f) * inv_cw), j = idx - m * cw;
-      float sum = 0.f;
-      for (int r = 0; r < nslots; ++r) sum += red[(r * plan.xrows + m) * cw + j];
-      if (nbase + j < p.N) p.y[static_cast<size_t>(m0 + m) * p.ldy + nbase + j] = float_to_out<BF16>(sum);
+    if constexpr (!AR) {
+      for (int idx = threadIdx.x; idx < mvalid * cw; idx += blockDim.x) {
+        const int m = static_cast<int>((static_cast<float>(idx) + 0.5f) * inv_cw), j = idx - m * cw;
+        float sum = 0.f;
+        for (int r = 0; r < nslots; ++r) sum += red[(r * plan.xrows + m) * cw + j];
+        if (nbase + j < p.N) p.y[static_cast<size_t>(m0 + m) * p.ldy + nbase + j] = float_to_out<BF16>(sum);
+      }
+    } else {
+      // ---- all-reduce over peer memory, fused: this CTA's column block of this rank's partial product ----
+      const unsigned epoch = *reinterpret_cast<volatile unsigned *>(ar->ctrl) + 1u;  // the previous reduction has finished (stream order)
+      const int set = static_cast<int>(epoch & 1u);
+      const int nr = ar->nranks;
+      const long long my_slot = (static_cast<long long>(set) * nr + ar->rank) * ar->slot_elems;
+      // 1. store the partial sums into this rank's slot on every rank
+      for (int idx = threadIdx.x; idx < mvalid * cw; idx += blockDim.x) {
+        const int m = static_cast<int>((static_cast<float>(idx) + 0.5f) * inv_cw), j = idx - m * cw;
+        float sum = 0.f;
+        for (int r = 0; r < nslots; ++r) sum += red[(r * plan.xrows + m) * cw + j];
+        if (nbase + j < p.N) {
+          const long long off = my_slot + static_cast<long long>(m0 + m) * p.N + nbase + j;
+          for (int q = 0; q < nr; ++q) ar->data[q][off] = sum;
+        }
+      }
+      __threadfence_system();
+      __syncthreads();
+      // 2. publish: one flag per (slot set, source rank, CTA) on every rank, carrying the epoch
+      const unsigned cta_id = blockIdx.y * gridDim.x + blockIdx.x;
+      if (threadIdx.x < nr)
+        st_release_sys(ar->flags[threadIdx.x] + (static_cast<long long>(set) * nr + ar->rank) * kArMaxBlocks + cta_id, epoch);
+      if (!ar->push_only) {
+        // 3. wait for the same block of every other rank (bounded: a rank that never arrives is reported, not waited for)
+        if (threadIdx.x < nr) {
+          const unsigned *flag = ar->flags[ar->rank] + (static_cast<long long>(set) * nr + threadIdx.x) * kArMaxBlocks + cta_id;
+          bool ok = false;
+          for (unsigned it = 0; it < (1u << 21); ++it) {
+            if (ld_acquire_sys(flag) == epoch) {
+              ok = true;
+              break;
+            }
+            if (it > 8) __nanosleep(64);
+          }
+          if (!ok) report_status(kStatusPeerTimeout);
+        }
+        __syncthreads();
+        // 4. add the slots in rank order (every rank adds the same numbers in the same order) and write the output
+        const float *mine = ar->data[ar->rank] + static_cast<long long>(set) * nr * ar->slot_elems;
+        for (int idx = threadIdx.x; idx < mvalid * cw; idx += blockDim.x) {
+          const int m = static_cast<int>((static_cast<float>(idx) + 0.5f) * inv_cw), j = idx - m * cw;
+          if (nbase + j < p.N) {
+            const long long off = static_cast<long long>(m0 + m) * p.N + nbase + j;
+            float sum = 0.f;
+            for (int r = 0; r < nr; ++r) sum += __ldcg(mine + r * ar->slot_elems + off);
+            p.y[static_cast<size_t>(m0 + m) * p.ldy + nbase + j] = float_to_out<BF16>(sum);
+          }
+        }
+      }
+      // 5. the last CTA of the launch closes the epoch (with push_only the finishing kernel does)
+      __syncthreads();
+      if (threadIdx.x == 0) {
+        const unsigned total = gridDim.x * gridDim.y;
+        __threadfence();
+        const unsigned ticket = atomicAdd(ar->ctrl + 1, 1u);
+        if (ticket == total - 1) {
+          ar->ctrl[1] = 0;
+          ar->ctrl[2] = total;
+          __threadfence();
+          if (!ar->push_only) *reinterpret_cast<volatile unsigned *>(ar->ctrl) = epoch;
+        }
+      }
     }
   }
 }
@@ -567,6 +640,45 @@ __global__ void __launch_bounds__(512, 1) gemv_kernel(const GemvParams p) {
 }
 
 #if !MG_GEMV_ZP
+// Row-parallel product fused with the all-reduce of its output (group size 128; see ArParams in kernels.h).
+template <int B, bool BF16, int NT>
+__global__ void __launch_bounds__(512, 1) gemv_allreduce_kernel(const GemvParams p, const ArParams ar) {
+  gemv_body<B, 128, BF16, NT, false, true>(p, static_cast<int>(blockIdx.x), &ar);
+}
+
+// Second half of the protocol as a kernel of its own, for launches made with push_only (one GPU standing in for all
+// ranks: the ranks' products run one after the other, so nothing may wait inside them): checks that every
+// block of every rank has been published for the current epoch, adds the slots in rank order, closes the epoch.
+template <bool BF16>
+__global__ void allreduce_finish_kernel(const ArParams ar, uint16_t *y, int N, int M) {
+  const unsigned epoch = *reinterpret_cast<volatile unsigned *>(ar.ctrl) + 1u;
+  const int set = static_cast<int>(epoch & 1u);
+  const unsigned blocks = ar.ctrl[2];
+  const long long tid = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  const long long nthreads = static_cast<long long>(gridDim.x) * blockDim.x;
+  for (long long i = tid; i < static_cast<long long>(ar.nranks) * blocks; i += nthreads) {
+    const int r = static_cast<int>(i / blocks);
+    const unsigned b = static_cast<unsigned>(i - static_cast<long long>(r) * blocks);
+    if (ld_acquire_sys(ar.flags[ar.rank] + (static_cast<long long>(set) * ar.nranks + r) * kArMaxBlocks + b) != epoch)
+      report_status(kStatusPeerTimeout);
+  }
+  const float *mine = ar.data[ar.rank] + static_cast<long long>(set) * ar.nranks * ar.slot_elems;
+  for (long long i = tid; i < static_cast<long long>(M) * N; i += nthreads) {
+    float sum = 0.f;
+    for (int r = 0; r < ar.nranks; ++r) sum += __ldcg(mine + r * ar.slot_elems + i);
+    y[i] = float_to_out<BF16>(sum);
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();
+    if (atomicAdd(ar.ctrl + 1, 1u) == gridDim.x - 1) {
+      ar.ctrl[1] = 0;
+      __threadfence();
+      *reinterpret_cast<volatile unsigned *>(ar.ctrl) = epoch;
+    }
+  }
+}
+
 // ----------------------------------------------------------------------------
 // Grouped launch: several products over the SAME activations in one kernel, each with its own packed
 // weights, scales, out-features and bitwidth, written side by side into one output [M, sum N_i].  This is
@@ -811,6 +923,123 @@ int MG_GEMV_LAUNCH(int bitwidth, int group_size, int N, int K, int M, const void
 }
 
 #if !MG_GEMV_ZP
+// ---- product + all-reduce, host side -----------------------------------------------------------------------
+template <int B, bool BF16, int NT>
+static int launch_allreduce(GemvParams p, const ArParams &ar, const GemvShape &c, cudaStream_t stream, bool pdl) {
+  auto kernel = gemv_allreduce_kernel<B, BF16, NT>;
+  const int R = c.R, S = c.S, RK = c.RK;
+  if (R < 1 || R > 16 || S < 1 || S > 8 || (S & (S - 1)) != 0 || S > p.kblocks) return MG_ERR_UNSUPPORTED;
+  if (RK < 1 || R % RK != 0 || RK > p.kblocks / S || (R / RK) * 16 % S != 0) return MG_ERR_UNSUPPORTED;
+  p.split = S;
+  p.kslices = RK;
+  const int max_nblk = (p.kblocks + S - 1) / S;
+  const int ctas_per_sm = R >= 16 ? 1 : 16 / R;
+  const int budget = smem_for_ctas_per_sm(ctas_per_sm);
+  const int nchunks = (max_nblk + ChunkBlocks<B, NT>::value - 1) / ChunkBlocks<B, NT>::value;
+  int xblocks = max_nblk;
+  if (make_plan<B, 128, NT, false>(R, p.M, max_nblk, 2, xblocks).total > budget) {
+    if (RK > 1) return MG_ERR_UNSUPPORTED;
+    xblocks = (NT == 1) ? 8 : 4;
+  }
+  if (xblocks > max_nblk) xblocks = max_nblk;
+  int stages = 2;
+  while (stages < 8 && stages < nchunks && make_plan<B, 128, NT, false>(R, p.M, max_nblk, stages + 1, xblocks).total <= budget) ++stages;
+  p.stages = stages;
+  p.xblocks = xblocks;
+  const SmemPlan plan = make_plan<B, 128, NT, false>(R, p.M, max_nblk, stages, xblocks);
+  if (plan.total > 227 * 1024 - 1024) return MG_ERR_UNSUPPORTED;
+  const int floor_bytes = smem_for_ctas_per_sm(ctas_per_sm + 1) + 1;
+  const size_t smem = static_cast<size_t>(plan.total > floor_bytes ? plan.total : floor_bytes);
+  if (smem > 48 * 1024) {
+    static SharedMemoryOptIn opt_in;
+    const int st = opt_in.ensure(kernel, 226 * 1024);
+    if (st != MG_OK) return st;
+  }
+  const int Rt = R / RK;
+  const int row_groups = (p.tiles + Rt - 1) / Rt;
+  const int passes = (p.M + NT * 8 - 1) / (NT * 8);
+  if (static_cast<long long>(row_groups) * S * passes > kArMaxBlocks) return MG_ERR_UNSUPPORTED;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(row_groups * S, passes, 1);
+  cfg.blockDim = dim3(R * 32, 1, 1);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attrs[2];
+  int na = 0;
+  if (S > 1) {
+    attrs[na].id = cudaLaunchAttributeClusterDimension;
+    attrs[na].val.clusterDim.x = S;
+    attrs[na].val.clusterDim.y = 1;
+    attrs[na].val.clusterDim.z = 1;
+    ++na;
+  }
+  if (pdl) {
+    attrs[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attrs[na].val.programmaticStreamSerializationAllowed = 1;
+    ++na;
+  }
+  cfg.attrs = attrs;
+  cfg.numAttrs = na;
+  return cudaLaunchKernelEx(&cfg, kernel, p, ar) == cudaSuccess ? MG_OK : MG_ERR_CUDA;
+}
+
+template <int B>
+static int launch_allreduce_b(const GemvParams &p, const ArParams &ar, const GemvShape &c, bool bf16, cudaStream_t stream, bool pdl) {
+  if (p.M <= 8)
+    return bf16 ? launch_allreduce<B, true, 1>(p, ar, c, stream, pdl) : launch_allreduce<B, false, 1>(p, ar, c, stream, pdl);
+  return bf16 ? launch_allreduce<B, true, 2>(p, ar, c, stream, pdl) : launch_allreduce<B, false, 2>(p, ar, c, stream, pdl);
+}
+
+// MG_ERR_UNSUPPORTED (nothing launched, nothing published) for group sizes other than 128 and shapes that do not fit.
+int gemv_allreduce_launch(int bitwidth, int group_size, int N, int K, int M, const void *w, const void *s, const void *x,
+                          void *y, bool bf16, bool pdl, const ArParams &ar, cudaStream_t stream) {
+  if (group_size != 128 || ar.nranks < 1 || ar.nranks > kArMaxRanks || ar.rank < 0 || ar.rank >= ar.nranks) return MG_ERR_UNSUPPORTED;
+  if (static_cast<long long>(M) * N > ar.slot_elems) return MG_ERR_UNSUPPORTED;
+  int sm_count = 0;
+  {
+    const int st = current_device_sm_count(&sm_count);
+    if (st != MG_OK) return st;
+  }
+  GemvParams p;
+  p.w = static_cast<const uint32_t *>(w);
+  p.s = static_cast<const uint16_t *>(s);
+  p.z = nullptr;
+  p.x = static_cast<const uint16_t *>(x);
+  p.y = static_cast<uint16_t *>(y);
+  p.N = N;
+  p.K = K;
+  p.M = M;
+  p.ldy = N;
+  p.tiles = N / 16;
+  p.kblocks = K / 128;
+  GemvShape first, second;
+  gemv_pick_config(p.tiles, p.kblocks, M < 16 ? M : 16, sm_count, &first, &second);
+  auto launch = [&](const GemvShape &c) {
+    switch (bitwidth) {
+      case 2: return launch_allreduce_b<2>(p, ar, c, bf16, stream, pdl);
+      case 3: return launch_allreduce_b<3>(p, ar, c, bf16, stream, pdl);
+      case 4: return launch_allreduce_b<4>(p, ar, c, bf16, stream, pdl);
+      case 6: return launch_allreduce_b<6>(p, ar, c, bf16, stream, pdl);
+      case 8: return launch_allreduce_b<8>(p, ar, c, bf16, stream, pdl);
+      default: return static_cast<int>(MG_ERR_BAD_ARG);
+    }
+  };
+  int r = launch(first);
+  if (r == MG_ERR_UNSUPPORTED) r = launch(second);
+  return r;
+}
+
+int allreduce_finish_launch(const ArParams &ar, void *y, int N, int M, bool bf16, cudaStream_t stream) {
+  long long blocks = (static_cast<long long>(M) * N + 255) / 256;
+  if (blocks > 148 * 4) blocks = 148 * 4;
+  if (blocks < 1) blocks = 1;
+  if (bf16)
+    allreduce_finish_kernel<true><<<static_cast<unsigned>(blocks), 256, 0, stream>>>(ar, static_cast<uint16_t *>(y), N, M);
+  else
+    allreduce_finish_kernel<false><<<static_cast<unsigned>(blocks), 256, 0, stream>>>(ar, static_cast<uint16_t *>(y), N, M);
+  return cudaGetLastError() == cudaSuccess ? MG_OK : MG_ERR_CUDA;
+}
+
 // ---- grouped launch, host side --------------------------------------------------------------------------
 template <int GS, int NT> static SmemPlan plan_for_bits(int bits, int R, int M, int max_nblk, int stages, int xblocks) {
   switch (bits) {

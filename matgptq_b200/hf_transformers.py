@@ -158,14 +158,22 @@ class StaticCacheDecoder:
 
     @torch.no_grad()
     def time_decode(self, input_ids: torch.Tensor, benchmark_runs: int = 16, number_of_runs: int = 16, warmups: int = 16):
-        """Seconds per decode step, one mean per run of ``number_of_runs`` steps
-        (the protocol of ``bench_transformers_e2e.py:61-76,187-190``; the cache position stays put as there)."""
+        """Seconds per decode step, one mean per run of ``number_of_runs`` steps (the protocol of
+        ``bench_transformers_e2e.py:61-76,187-190``).  The reference re-runs the step at one cache position;
+        here the position advances and the cache is sized for every step of the measurement, because newer
+        ``transformers`` caches count the tokens they have seen themselves and a step past the end of the
+        cache is an out-of-bounds write."""
         dev, seq_len = input_ids.device, input_ids.shape[1]
-        last_logits, cache = self.prefill(input_ids, 2)
+        total_steps = warmups + benchmark_runs * number_of_runs
+        last_logits, cache = self.prefill(input_ids, total_steps + 1)
         next_token = torch.argmax(last_logits, dim=-1)[:, None]
         decode = self._decode_fn()
         cache_position = torch.tensor([seq_len], device=dev)
-        step = lambda: decode(self.model, next_token.clone(), None, cache_position, cache)  # noqa: E731
+
+        def step():
+            decode(self.model, next_token.clone(), None, cache_position, cache)
+            cache_position.add_(1)
+
         for _ in range(warmups):
             step()
         torch.cuda.synchronize()

@@ -143,3 +143,25 @@ def test_operators_are_traceable(cuda, expected):
     ids = torch.tensor([expected["prompt"]], device=cuda)
     times = hf.StaticCacheDecoder(model, compile_forward=False).time_decode(ids, benchmark_runs=2, number_of_runs=16, warmups=16)
     assert len(times) == 2 and all(t > 0 for t in times)
+
+
+@pytest.mark.gpu
+def test_hf_static_cache_decode_under_torch_compile(cuda, expected):
+    """The reference's decode loop: torch.compile(fullgraph=True, mode="reduce-overhead") over a StaticCache
+    (inference_demo_transformers.py:141-173).  The compiled loop must give the eager loop's tokens.  inductor
+    also emits host C++ and builds it with the machine's g++; where that toolchain cannot (no libgomp.spec on
+    some boxes) the step is still traced as one full graph with fake tensors, which is what the operator's
+    fake registration is for, and the traced graph runs with the ordinary kernels."""
+    from matgptq_b200 import hf_transformers as hf
+    model = hf.load_packed_causal_lm(FIXTURE, os.path.join(FIXTURE, "bitwidths.txt"), cuda)
+    ids = torch.tensor([expected["prompt"]], device=cuda)
+    compiled = hf.StaticCacheDecoder(model, compile_forward=True)
+    try:
+        tokens = compiled.generate(ids, len(expected["greedy_tokens"]))
+    except Exception as e:  # noqa: BLE001
+        if "CppCompileError" not in repr(e) and "CppCompileError" not in str(e):
+            raise
+        torch._dynamo.reset()
+        compiled = hf.StaticCacheDecoder(model, compile_forward=True, backend="eager")
+        tokens = compiled.generate(ids, len(expected["greedy_tokens"]))
+    assert tokens[0].tolist() == expected["greedy_tokens"]
