@@ -245,8 +245,13 @@ def start_watchdog(stall_seconds: float, total_seconds: float) -> None:
     threading.Thread(target=bark, daemon=True).start()
 
 
-def launch_cell(c, flags: int, world: int):
+def launch_cell(c, flags: int, world: int, peer=None):
+    """One cell; with several ranks the row-parallel cells include the all-reduce of their output: fused into
+    the product's epilogue over peer memory (`peer`, a tp_comm.PeerAllReduce), or NCCL behind the product."""
     from matgptq_b200 import ops
+    if world > 1 and ROW_PARALLEL[c["name"]] and peer is not None:
+        peer.matmul(c["x"], c["packed"], c["scales"], c["n_loc"], c["k_loc"], c["b"], GROUP, flags, out=c["y"])
+        return
     ops.matmul_matgptq_raw(c["x"], c["packed"], c["scales"], c["n_loc"], c["k_loc"], c["b"], GROUP, flags, out=c["y"])
     if world > 1 and ROW_PARALLEL[c["name"]]:
         torch.distributed.all_reduce(c["y"])
@@ -376,6 +381,11 @@ def ours_main(args) -> None:
     from matgptq_b200 import _native, ops  # noqa: F401
 
     flags = _native.FLAG_ASYNC | (_native.FLAG_PDL if not args.no_pdl else 0)
+    peer = None
+    if world > 1 and args.allreduce == "fused":
+        from matgptq_b200.tp_comm import PeerAllReduce
+        progress("setting up the peer-memory buffers")
+        peer = PeerAllReduce(device=dev, max_rows=32, max_cols=8192)
     progress("process group up, building cells")
     cells = build_cells(world, rank, dev)
     progress("cells built")
@@ -383,16 +393,24 @@ def ours_main(args) -> None:
     launches_per_step = len(cells)
 
     stream = torch.cuda.Stream(device=dev)
+    if world > 1:
+        # the fused all-reduce waits for its peers inside the kernel, with a bound of about a second: the ranks
+        # have to enter each phase together
+        torch.cuda.synchronize()
+        torch.distributed.barrier()
     with torch.cuda.stream(stream):
         for c in cells:  # eager pass: loads kernels, NCCL channels
-            launch_cell(c, flags, world)
+            launch_cell(c, flags, world, peer)
         stream.synchronize()
         progress("eager pass done")
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(graph, stream=stream):
             for c in cells:
-                launch_cell(c, flags, world)
+                launch_cell(c, flags, world, peer)
         progress("graph captured")
+        if world > 1:
+            stream.synchronize()
+            torch.distributed.barrier()
         sampler = ClockSampler(local_rank)
         if rank == 0:
             sampler.start()
@@ -461,7 +479,7 @@ def ours_main(args) -> None:
     progress("sweep finished")
     if not args.no_decode:
         # mixed-precision decode, Llama-3.1-8B architecture, mean 3.0 bits, prompt 128, 128 new tokens
-        dec = [run_decode(world, rank, dev, "8b", batch, 128, 128, 3.0) for batch in ((1, 8, 32) if world == 1 else (1,))]
+        dec = [run_decode(world, rank, dev, "8b", batch, 128, 128, 3.0, peer=peer) for batch in ((1, 8, 32) if world == 1 else (1,))]
         extra["decode"] = dec
 
     if rank != 0:
@@ -476,7 +494,8 @@ def ours_main(args) -> None:
         "config": {"workload": "llama3-8b linear shapes (q/o 4096x4096, k/v 4096x1024, gate/up 4096x14336, down 14336x4096) "
                                "x M{1,2,4,8,16} x b{2,3,4,6,8}, g128, fp16, sliced from 8-bit masters",
                    "cells_per_step": launches_per_step, "l2_policy": "inputs larger than L2: ~400 MB of other weights between reuses",
-                   "parallelism": "tp%d" % world if world > 1 else "single", "pdl": not args.no_pdl},
+                   "parallelism": "tp%d" % world if world > 1 else "single", "pdl": not args.no_pdl,
+                   "allreduce": ("fused into the row-parallel kernels over peer memory" if peer is not None else "nccl") if world > 1 else None},
         "clocks": clocks,
         "parity_checked": bool(parity and parity["checked_cells"] == launches_per_step and not parity["failed"]),
         "parity": parity,
@@ -501,7 +520,7 @@ def ours_main(args) -> None:
 
 
 def run_decode(world: int, rank: int, dev: torch.device, model_name: str, batch: int, prompt_len: int, new_tokens: int,
-               mean_bits: float, layers: int | None = None, uniform_bits: int = 0) -> dict:
+               mean_bits: float, layers: int | None = None, uniform_bits: int = 0, peer=None) -> dict:
     """Greedy decode of a random-init Llama-architecture model over packed linears: random prompt ids,
     seeded per-layer bitwidths from {2,3,4,6,8} with the given parameter-weighted mean, one CUDA-graph
     replay per token; tok/s = generated tokens * batch / device time of the decode phase (max over ranks)."""
@@ -517,7 +536,7 @@ def run_decode(world: int, rank: int, dev: torch.device, model_name: str, batch:
     achieved_bits = sum(bits[n] * names[n] for n in names) / sum(names.values())
     progress(f"decode: building {model_name} batch {batch}")
     model = decode.PackedLlama(shape, bits, dtype=torch.float16, tp_rank=rank, tp_size=world, seed=0, batch=batch,
-                               max_seq=prompt_len + new_tokens, device=dev)
+                               max_seq=prompt_len + new_tokens, device=dev, peer_allreduce=peer)
     progress("decode: model built")
     g = torch.Generator().manual_seed(0)
     prompt = torch.randint(0, shape.vocab, (batch, prompt_len), generator=g).to(dev)
@@ -672,10 +691,14 @@ def decode_main(args) -> None:
     if world > 1:
         progress("bringing the process group up")
         torch.distributed.init_process_group("nccl", device_id=dev)
+    peer = None
+    if world > 1 and args.allreduce == "fused":
+        from matgptq_b200.tp_comm import PeerAllReduce
+        peer = PeerAllReduce(device=dev, max_rows=32, max_cols=8192)
     parts = args.decode.split(":")
     uniform = int(parts[4][1:]) if parts[4].startswith("u") else 0  # "u4": every layer at 4 bits
     r = run_decode(world, rank, dev, parts[0], int(parts[1]), int(parts[2]), int(parts[3]),
-                   0.0 if uniform else float(parts[4]), int(parts[5]) if len(parts) > 5 else None, uniform_bits=uniform)
+                   0.0 if uniform else float(parts[4]), int(parts[5]) if len(parts) > 5 else None, uniform_bits=uniform, peer=peer)
     if rank == 0:
         print(json.dumps({"metric": "decode_tokens_per_s", "value": r["tok_per_s"], "unit": "tok/s", "n_gpus": world, **r}), flush=True)
     if world > 1:
@@ -695,6 +718,8 @@ def main() -> None:
                     help="seconds one phase may last before the run reports where it stands and exits 3 (0 = off)")
     ap.add_argument("--watchdog-total", type=float, default=900.0, help="the same for the whole run")
     ap.add_argument("--no-pdl", action="store_true", help="launch without programmatic dependent launch")
+    ap.add_argument("--allreduce", choices=["fused", "nccl"], default="fused",
+                    help="several ranks: all-reduce of the row-parallel layers fused into their kernels over peer memory, or NCCL")
     ap.add_argument("--no-table", action="store_true", help="skip the per-cell cold-L2 table")
     ap.add_argument("--no-check", action="store_true", help="skip the comparison of the sweep's outputs with the oracle")
     ap.add_argument("--no-decode", action="store_true", help="skip the whole-model decode measurement")

@@ -120,25 +120,25 @@ int matgptq_b200_matmul_grouped(const matgptq_b200_segment *segments, int n_segm
  * holds a K shard of the layer and calls this with its shard; all ranks pass the same n_out, batch, bitwidth and
  * a K shard of the same size).  In the reference this step is vLLM's: RowParallelLinear all-reduces what
  * MatGPTQLinearMethod.apply returns (inference_lib/vllm_matgptq.py:180-200 holds no collective), so the entry has
- * no counterpart there.  One kernel: the epilogue of every CTA stores its fp32 partial sums of a column block into
- * this rank's slot in EVERY rank's buffer (plain stores over NVLink to peer-mapped memory), publishes a flag,
- * waits for the other ranks' flags of the same block and adds the slots in rank order, so all ranks get the same
- * bits and y needs no further collective.  Waits are bounded: a rank that never arrives leaves status 105 in
+ * no counterpart there.  One kernel: in the epilogue every fp32 partial sum is stored, paired with the epoch of the
+ * call in one 8-byte store, into this rank's slot in every other rank's buffer (plain stores over NVLink to
+ * peer-mapped memory); the same thread then reads the other ranks' values of that output from its own buffer,
+ * polling until each carries the epoch, and adds them in rank order, so all ranks get the same bits and y needs no
+ * further collective.  Waits are bounded (about a second): a rank that never arrives leaves status 105 in
  * matgptq_b200_device_status instead of a hung GPU.
- *   comm.data[q], comm.flags[q]: device addresses, valid on THIS device, of rank q's buffers (this rank's own for
- *       q == rank, peer mappings otherwise): data 2*nranks*slot_elems floats, flags 2*nranks*4096 uint32.  All zero
- *       before the first call.  Two slot sets alternate from call to call, so the buffers serve every layer.
+ *   comm.data[q]: device address, valid on THIS device, of rank q's buffer (this rank's own for q == rank, a peer
+ *       mapping otherwise): 2*nranks*slot_elems 8-byte words, all zero before the first call, 8-byte aligned.  Two
+ *       slot sets alternate from call to call, so one buffer serves every layer.
  *   comm.ctrl: 4 uint32 in this rank's own memory, zero before the first call.
  *   comm.slot_elems >= batch * n_out.
- *   comm.push_only: store and publish only; matgptq_b200_allreduce_finish then adds up.  For running all ranks one
- *       after the other on one GPU (tests): kernels that wait for each other must not be separate launches there.
- * Batches of 32 rows and more, group sizes other than 128 and shapes whose launch would exceed 4096 CTAs return
- * MATGPTQ_B200_ERR_UNSUPPORTED with nothing launched: run matgptq_b200_matmul and a library all-reduce instead.
- * Calls on one communicator must be made in the same order on every rank, on one stream per rank.
+ *   comm.push_only: store only (also into the own slot); matgptq_b200_allreduce_finish then adds up.  For running all
+ *       ranks one after the other on one GPU (tests): kernels that wait for each other must not be separate launches.
+ * Batches of 32 rows and more and group sizes other than 128 return MATGPTQ_B200_ERR_UNSUPPORTED with nothing
+ * launched: run matgptq_b200_matmul and a library all-reduce instead.  Calls on one communicator must be made in
+ * the same order on every rank, on one stream per rank.
  */
 typedef struct {
   void *data[8];
-  void *flags[8];
   void *ctrl;
   int64_t slot_elems;
   int rank, nranks;
@@ -147,8 +147,8 @@ typedef struct {
 int matgptq_b200_matmul_allreduce(int64_t bitwidth, int64_t group_size, int64_t n_out, int64_t n_in_shard, int64_t batch,
                                   const void *w, const void *s, const void *x, void *y, void *stream, uint32_t flags,
                                   const matgptq_b200_comm *comm);
-/* Adds up what launches with comm.push_only published (every rank's block flags are checked, status 105 if one is
- * missing) into y[batch, n_out] and closes the epoch. */
+/* Adds up what launches with comm.push_only stored (status 105 if a value of some rank is missing) into
+ * y[batch, n_out] and closes the epoch. */
 int matgptq_b200_allreduce_finish(const matgptq_b200_comm *comm, void *y, int64_t n_out, int64_t batch, void *stream,
                                   uint32_t flags);
 

@@ -29,7 +29,7 @@ class Segment(ctypes.Structure):
 
 class Comm(ctypes.Structure):
     """``matgptq_b200_comm`` of the C header: peer buffers of the fused row-parallel product + all-reduce."""
-    _fields_ = [("data", ctypes.c_void_p * 8), ("flags", ctypes.c_void_p * 8), ("ctrl", ctypes.c_void_p),
+    _fields_ = [("data", ctypes.c_void_p * 8), ("ctrl", ctypes.c_void_p),
                 ("slot_elems", ctypes.c_int64), ("rank", ctypes.c_int), ("nranks", ctypes.c_int), ("push_only", ctypes.c_int)]
 
 

@@ -176,9 +176,8 @@ static int to_ar_params(const matgptq_b200_comm *comm, mg::ArParams *ar) {
       !comm->ctrl || comm->slot_elems <= 0)
     return MG_ERR_BAD_ARG;
   for (int q = 0; q < comm->nranks; ++q) {
-    if (!comm->data[q] || !comm->flags[q]) return MG_ERR_BAD_ARG;
-    ar->data[q] = static_cast<float *>(comm->data[q]);
-    ar->flags[q] = static_cast<unsigned *>(comm->flags[q]);
+    if (!comm->data[q] || (reinterpret_cast<uintptr_t>(comm->data[q]) & 7u)) return MG_ERR_BAD_ARG;
+    ar->data[q] = static_cast<uint2 *>(comm->data[q]);
   }
   ar->ctrl = static_cast<unsigned *>(comm->ctrl);
   ar->slot_elems = comm->slot_elems;

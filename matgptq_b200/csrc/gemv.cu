@@ -105,12 +105,13 @@ __host__ __device__ inline SmemPlan make_plan(int R, int M, int max_nblk, int st
 // NT: batch tiles of 8 rows handled per pass.
 // The whole computation of one CTA; `block_x` is the CTA's index among the CTAs of this product (blockIdx.x for a
 // plain launch, the index inside its segment for a grouped one).
-__device__ __forceinline__ void st_release_sys(unsigned *ptr, unsigned v) {
-  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(ptr), "r"(v) : "memory");
+// 8-byte accesses that are single transactions: a value and its flag travel and become visible together
+__device__ __forceinline__ void st_volatile_v2(uint2 *ptr, uint2 v) {
+  asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(ptr), "r"(v.x), "r"(v.y) : "memory");
 }
-__device__ __forceinline__ unsigned ld_acquire_sys(const unsigned *ptr) {
-  unsigned v;
-  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(ptr) : "memory");
+__device__ __forceinline__ uint2 ld_volatile_v2(const uint2 *ptr) {
+  uint2 v;
+  asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(ptr) : "memory");
   return v;
 }
 
@@ -572,51 +573,41 @@ __device__ __forceinline__ void gemv_body(const GemvParams &p, const int block_x
       // ---- all-reduce over peer memory, fused: this CTA's column block of this rank's partial product ----
       const unsigned epoch = *reinterpret_cast<volatile unsigned *>(ar->ctrl) + 1u;  // the previous reduction has finished (stream order)
       const int set = static_cast<int>(epoch & 1u);
-      const int nr = ar->nranks;
-      const long long my_slot = (static_cast<long long>(set) * nr + ar->rank) * ar->slot_elems;
-      // 1. store the partial sums into this rank's slot on every rank
+      const int nr = ar->nranks, me = ar->rank;
+      const long long set_base = static_cast<long long>(set) * nr * ar->slot_elems;
+      const uint2 *mine = ar->data[me] + set_base;  // what the other ranks store for this rank
+      bool late = false;
       for (int idx = threadIdx.x; idx < mvalid * cw; idx += blockDim.x) {
         const int m = static_cast<int>((static_cast<float>(idx) + 0.5f) * inv_cw), j = idx - m * cw;
         float sum = 0.f;
         for (int r = 0; r < nslots; ++r) sum += red[(r * plan.xrows + m) * cw + j];
-        if (nbase + j < p.N) {
-          const long long off = my_slot + static_cast<long long>(m0 + m) * p.N + nbase + j;
-          for (int q = 0; q < nr; ++q) ar->data[q][off] = sum;
-        }
-      }
-      __threadfence_system();
-      __syncthreads();
-      // 2. publish: one flag per (slot set, source rank, CTA) on every rank, carrying the epoch
-      const unsigned cta_id = blockIdx.y * gridDim.x + blockIdx.x;
-      if (threadIdx.x < nr)
-        st_release_sys(ar->flags[threadIdx.x] + (static_cast<long long>(set) * nr + ar->rank) * kArMaxBlocks + cta_id, epoch);
-      if (!ar->push_only) {
-        // 3. wait for the same block of every other rank (bounded: a rank that never arrives is reported, not waited for)
-        if (threadIdx.x < nr) {
-          const unsigned *flag = ar->flags[ar->rank] + (static_cast<long long>(set) * nr + threadIdx.x) * kArMaxBlocks + cta_id;
-          bool ok = false;
-          for (unsigned it = 0; it < (1u << 21); ++it) {
-            if (ld_acquire_sys(flag) == epoch) {
-              ok = true;
-              break;
-            }
-            if (it > 8) __nanosleep(64);
+        if (nbase + j >= p.N) continue;
+        const long long off = static_cast<long long>(m0 + m) * p.N + nbase + j;
+        // 1. value and epoch in one 8-byte store into this rank's slot on every other rank
+        const uint2 packet = make_uint2(__float_as_uint(sum), epoch);
+        for (int q = 0; q < nr; ++q)
+          if (q != me || ar->push_only) st_volatile_v2(ar->data[q] + set_base + me * ar->slot_elems + off, packet);
+        if (ar->push_only) continue;
+        // 2. the other ranks' values of the same output, in rank order (every rank adds the same numbers in the
+        //    same order); a word that does not show the epoch within about a second is reported, not waited for
+        float total = 0.f;
+        for (int r = 0; r < nr; ++r) {
+          if (r == me) {
+            total += sum;
+            continue;
           }
-          if (!ok) report_status(kStatusPeerTimeout);
-        }
-        __syncthreads();
-        // 4. add the slots in rank order (every rank adds the same numbers in the same order) and write the output
-        const float *mine = ar->data[ar->rank] + static_cast<long long>(set) * nr * ar->slot_elems;
-        for (int idx = threadIdx.x; idx < mvalid * cw; idx += blockDim.x) {
-          const int m = static_cast<int>((static_cast<float>(idx) + 0.5f) * inv_cw), j = idx - m * cw;
-          if (nbase + j < p.N) {
-            const long long off = static_cast<long long>(m0 + m) * p.N + nbase + j;
-            float sum = 0.f;
-            for (int r = 0; r < nr; ++r) sum += __ldcg(mine + r * ar->slot_elems + off);
-            p.y[static_cast<size_t>(m0 + m) * p.ldy + nbase + j] = float_to_out<BF16>(sum);
+          const uint2 *src = mine + r * ar->slot_elems + off;
+          uint2 v = ld_volatile_v2(src);
+          for (unsigned it = 0; v.y != epoch && it < (1u << 22); ++it) {
+            if (it > 16) __nanosleep(it < 4096 ? 32 : 256);
+            v = ld_volatile_v2(src);
           }
+          if (v.y != epoch) late = true;
+          total += __uint_as_float(v.x);
         }
+        p.y[static_cast<size_t>(m0 + m) * p.ldy + nbase + j] = float_to_out<BF16>(total);
       }
+      if (late) report_status(kStatusPeerTimeout);
       // 5. the last CTA of the launch closes the epoch (with push_only the finishing kernel does)
       __syncthreads();
       if (threadIdx.x == 0) {
@@ -625,7 +616,6 @@ __device__ __forceinline__ void gemv_body(const GemvParams &p, const int block_x
         const unsigned ticket = atomicAdd(ar->ctrl + 1, 1u);
         if (ticket == total - 1) {
           ar->ctrl[1] = 0;
-          ar->ctrl[2] = total;
           __threadfence();
           if (!ar->push_only) *reinterpret_cast<volatile unsigned *>(ar->ctrl) = epoch;
         }
@@ -647,27 +637,26 @@ __global__ void __launch_bounds__(512, 1) gemv_allreduce_kernel(const GemvParams
 }
 
 // Second half of the protocol as a kernel of its own, for launches made with push_only (one GPU standing in for all
-// ranks: the ranks' products run one after the other, so nothing may wait inside them): checks that every
-// block of every rank has been published for the current epoch, adds the slots in rank order, closes the epoch.
+// ranks: the ranks' products run one after the other, so nothing may wait inside them): adds the slots in rank
+// order, reports any value that does not carry the current epoch, closes the epoch.
 template <bool BF16>
 __global__ void allreduce_finish_kernel(const ArParams ar, uint16_t *y, int N, int M) {
   const unsigned epoch = *reinterpret_cast<volatile unsigned *>(ar.ctrl) + 1u;
   const int set = static_cast<int>(epoch & 1u);
-  const unsigned blocks = ar.ctrl[2];
   const long long tid = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
   const long long nthreads = static_cast<long long>(gridDim.x) * blockDim.x;
-  for (long long i = tid; i < static_cast<long long>(ar.nranks) * blocks; i += nthreads) {
-    const int r = static_cast<int>(i / blocks);
-    const unsigned b = static_cast<unsigned>(i - static_cast<long long>(r) * blocks);
-    if (ld_acquire_sys(ar.flags[ar.rank] + (static_cast<long long>(set) * ar.nranks + r) * kArMaxBlocks + b) != epoch)
-      report_status(kStatusPeerTimeout);
-  }
-  const float *mine = ar.data[ar.rank] + static_cast<long long>(set) * ar.nranks * ar.slot_elems;
+  const uint2 *mine = ar.data[ar.rank] + static_cast<long long>(set) * ar.nranks * ar.slot_elems;
+  bool missing = false;
   for (long long i = tid; i < static_cast<long long>(M) * N; i += nthreads) {
     float sum = 0.f;
-    for (int r = 0; r < ar.nranks; ++r) sum += __ldcg(mine + r * ar.slot_elems + i);
+    for (int r = 0; r < ar.nranks; ++r) {
+      const uint2 v = ld_volatile_v2(mine + r * ar.slot_elems + i);
+      if (v.y != epoch) missing = true;
+      sum += __uint_as_float(v.x);
+    }
     y[i] = float_to_out<BF16>(sum);
   }
+  if (missing) report_status(kStatusPeerTimeout);
   __syncthreads();
   if (threadIdx.x == 0) {
     __threadfence();
@@ -958,7 +947,6 @@ static int launch_allreduce(GemvParams p, const ArParams &ar, const GemvShape &c
   const int Rt = R / RK;
   const int row_groups = (p.tiles + Rt - 1) / Rt;
   const int passes = (p.M + NT * 8 - 1) / (NT * 8);
-  if (static_cast<long long>(row_groups) * S * passes > kArMaxBlocks) return MG_ERR_UNSUPPORTED;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(row_groups * S, passes, 1);
   cfg.blockDim = dim3(R * 32, 1, 1);

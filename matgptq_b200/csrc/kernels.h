@@ -23,19 +23,19 @@ int gemv_zp_launch(int bitwidth, int group_size, int N, int K, int M, const void
                    int ldy = 0);
 
 // Row-parallel product fused with its all-reduce over peer memory (gemv.cu).  Every rank runs the same launch on
-// its K shard; the epilogue of each CTA stores its fp32 partial sums of a column block into this rank's slot on
-// EVERY rank (plain stores to peer memory), publishes a per-block flag carrying the epoch, waits (bounded) for the
-// flags of the other ranks' same block and adds the slots in rank order, so every rank computes the same bits.
-// Two slot sets alternate by epoch parity; epochs only grow, so nothing is ever reset.
+// its K shard.  In the epilogue every thread stores each of its fp32 partial sums, paired with the epoch of the
+// call in ONE 8-byte store, into this rank's slot on every other rank (plain stores to peer memory), then reads
+// the other ranks' values of the same outputs from its own memory, polling each 8-byte word until it carries
+// the epoch (bounded), and adds them in rank order: every rank computes the same bits.  Value and flag travel
+// together, so no fence and no second round trip is needed.  Two slot sets alternate by epoch parity and epochs
+// only grow, so nothing is ever reset.
 constexpr int kArMaxRanks = 8;
-constexpr int kArMaxBlocks = 4096;  // flags per (slot set, rank): CTAs of one launch
 struct ArParams {
-  float *data[kArMaxRanks];      // rank q's buffer: [2][nranks][slot_elems] fp32
-  unsigned *flags[kArMaxRanks];  // rank q's flags:  [2][nranks][kArMaxBlocks]
-  unsigned *ctrl;                // local: [0] epoch of the last finished reduction, [1] CTA tickets, [2] CTAs of the last launch
-  long long slot_elems;          // elements of one slot (>= M * N)
+  uint2 *data[kArMaxRanks];  // rank q's buffer: [2][nranks][slot_elems] of {value bits, epoch}
+  unsigned *ctrl;            // local: [0] epoch of the last finished reduction, [1] CTA tickets
+  long long slot_elems;      // elements of one slot (>= M * N)
   int rank, nranks;
-  int push_only;                 // 1: store and publish only; matgptq_b200_allreduce_finish adds up (single-GPU emulation of ranks)
+  int push_only;             // 1: store only (also into the own slot); matgptq_b200_allreduce_finish adds up (single-GPU emulation of ranks)
 };
 constexpr int kStatusPeerTimeout = 105;
 int gemv_allreduce_launch(int bitwidth, int group_size, int N, int K, int M, const void *w, const void *s, const void *x,

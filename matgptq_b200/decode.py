@@ -118,8 +118,12 @@ class PackedLlama:
 
     def __init__(self, shape: LlamaShape, bits, *, group_size: int = 128, dtype: torch.dtype = torch.float16,
                  tp_rank: int = 0, tp_size: int = 1, seed: int = 0, batch: int = 1, max_seq: int = 256,
-                 device: torch.device | str = "cuda", keep_master: bool = False, pdl: bool = True):
+                 device: torch.device | str = "cuda", keep_master: bool = False, pdl: bool = True, peer_allreduce=None):
+        """``peer_allreduce``: a ``tp_comm.PeerAllReduce`` of the tensor-parallel group.  With it the row-parallel
+        layers (o, down) run the product fused with its all-reduce over peer memory for fewer than 32 rows; without
+        it (and for larger batches) the product is followed by an NCCL all-reduce."""
         self.shape, self.dtype, self.dev = shape, dtype, torch.device(device)
+        self.peer_ar = peer_allreduce
         self.tp_rank, self.tp_size, self.batch, self.max_seq, self.pdl = tp_rank, tp_size, batch, max_seq, pdl
         T, r, d = tp_size, tp_rank, shape.head_dim
         assert shape.n_heads % T == 0 and shape.n_kv_heads % T == 0 and shape.intermediate % (T * 128) == 0
@@ -166,6 +170,16 @@ class PackedLlama:
             dist.all_reduce(t)
         return t
 
+    def row_parallel(self, layer: int, which: str, x: torch.Tensor) -> torch.Tensor:
+        """A row-parallel layer and the all-reduce of its output (vLLM's RowParallelLinear in the reference)."""
+        L = self.layers[layer][which]
+        if (self.tp_size > 1 and self.peer_ar is not None and len(L.parts) == 1
+                and self.peer_ar.fits(x.shape[0], L.n_out, L.group_size)):
+            rows, bits, packed, scales = L.parts[0]
+            flag = L.flag | (_native.FLAG_PDL if self.pdl else 0)
+            return self.peer_ar.matmul(x, packed, scales, rows, L.n_in, bits, L.group_size, flag)
+        return self._all_reduce(self.linear(layer, which, x))
+
     def forward(self, tokens: torch.Tensor, positions: torch.Tensor) -> torch.Tensor:
         """tokens [B, S] int64, positions [S] int64 (device) -> logits of the last position [B, vocab] (fp32)."""
         B, S = tokens.shape
@@ -194,11 +208,11 @@ class PackedLlama:
                                                    B, S, self.h_loc, self.kv_loc, d, self.max_seq, flag, stream), "rope_kv")
             att = F.scaled_dot_product_attention(q, self.k_cache[li], self.v_cache[li], attn_mask=mask, enable_gqa=True)
             att = att.transpose(1, 2).reshape(rows, self.h_loc * d)
-            o = self._all_reduce(self.linear(li, "o", att))
+            o = self.row_parallel(li, "o", att)
             add_norm(x, o, L["ln2"], h)
             gu = self.linear(li, "gate_up", h)
             _native.check(lib.matgptq_b200_silu_mul(gu.data_ptr(), act.data_ptr(), rows, act.shape[1], flag, stream), "silu_mul")
-            dn = self._all_reduce(self.linear(li, "down", act))
+            dn = self.row_parallel(li, "down", act)
             nxt = self.layers[li + 1]["ln1"] if li + 1 < len(self.layers) else self.final_norm
             add_norm(x, dn, nxt, h)
         last = h.view(B, S, H)[:, -1]

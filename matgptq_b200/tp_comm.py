@@ -15,9 +15,6 @@ import torch
 
 from . import _native
 
-_MAX_BLOCKS = 4096  # flags per (slot set, rank): kArMaxBlocks of the library
-
-
 class PeerAllReduce:
     """Buffers and handle of one tensor-parallel group.  ``max_rows * max_cols`` bounds ``batch * n_out`` of a call."""
 
@@ -30,17 +27,15 @@ class PeerAllReduce:
             raise ValueError("at most 8 ranks")
         self.device = device or torch.device("cuda", torch.cuda.current_device())
         self.slot_elems = int(max_rows) * int(max_cols)
-        data_bytes = 2 * self.nranks * self.slot_elems * 4
-        flag_bytes = 2 * self.nranks * _MAX_BLOCKS * 4
+        data_bytes = 2 * self.nranks * self.slot_elems * 8  # two slot sets of {value, epoch} words per rank
         # plain peer mappings are all the kernel needs; no NVLink multicast object is bound to the buffer
         os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
-        self._buf = symm_mem.empty(data_bytes + flag_bytes, dtype=torch.uint8, device=self.device)
+        self._buf = symm_mem.empty(data_bytes, dtype=torch.uint8, device=self.device)
         self._buf.zero_()
         self._handle = symm_mem.rendezvous(self._buf, group)
         ptrs = list(self._handle.buffer_ptrs)
         self._ctrl = torch.zeros(4, dtype=torch.int32, device=self.device)
-        self.comm = _make_comm([p for p in ptrs], [p + data_bytes for p in ptrs], self._ctrl.data_ptr(), self.slot_elems,
-                               self.rank, self.nranks, push_only=False)
+        self.comm = _make_comm(ptrs, self._ctrl.data_ptr(), self.slot_elems, self.rank, self.nranks, push_only=False)
         torch.cuda.synchronize(self.device)
         dist.barrier(group)  # every rank's buffer is zero before anybody stores into it
 
@@ -53,11 +48,10 @@ class PeerAllReduce:
         return fused_matmul(self.comm, x, packed, scales, n_out, n_in_shard, bitwidth, group_size, flags, out)
 
 
-def _make_comm(data_ptrs, flag_ptrs, ctrl_ptr, slot_elems, rank, nranks, push_only) -> _native.Comm:
+def _make_comm(data_ptrs, ctrl_ptr, slot_elems, rank, nranks, push_only) -> _native.Comm:
     comm = _native.Comm()
     for q in range(nranks):
         comm.data[q] = data_ptrs[q]
-        comm.flags[q] = flag_ptrs[q]
     comm.ctrl = ctrl_ptr
     comm.slot_elems = slot_elems
     comm.rank, comm.nranks, comm.push_only = rank, nranks, 1 if push_only else 0
@@ -82,11 +76,10 @@ class LoopbackRanks:
 
     def __init__(self, nranks: int, device: torch.device, max_rows: int = 32, max_cols: int = 8192):
         self.nranks, self.slot_elems = nranks, max_rows * max_cols
-        self.data = [torch.zeros(2 * nranks * self.slot_elems, dtype=torch.float32, device=device) for _ in range(nranks)]
-        self.flags = [torch.zeros(2 * nranks * _MAX_BLOCKS, dtype=torch.int32, device=device) for _ in range(nranks)]
+        self.data = [torch.zeros(2 * nranks * self.slot_elems, dtype=torch.int64, device=device) for _ in range(nranks)]
         self.ctrl = [torch.zeros(4, dtype=torch.int32, device=device) for _ in range(nranks)]
-        self.comms = [_make_comm([d.data_ptr() for d in self.data], [f.data_ptr() for f in self.flags],
-                                 self.ctrl[r].data_ptr(), self.slot_elems, r, nranks, push_only=True) for r in range(nranks)]
+        self.comms = [_make_comm([d.data_ptr() for d in self.data], self.ctrl[r].data_ptr(), self.slot_elems, r, nranks,
+                                 push_only=True) for r in range(nranks)]
 
     def push(self, rank: int, x, packed, scales, n_out, n_in_shard, bitwidth, group_size, flags):
         scratch = torch.empty((x.size(-2), n_out), dtype=x.dtype, device=x.device)  # a push-only launch writes no output
