@@ -480,6 +480,9 @@ def ours_main(args) -> None:
     if not args.no_decode:
         # mixed-precision decode, Llama-3.1-8B architecture, mean 3.0 bits, prompt 128, 128 new tokens
         dec = [run_decode(world, rank, dev, "8b", batch, 128, 128, 3.0, peer=peer) for batch in ((1, 8, 32) if world == 1 else (1,))]
+        if world > 1:
+            # tensor-parallel decode of the Llama-3.1-70B architecture: seeded 3.5-bit mixture, prompt 512, 256 new tokens
+            dec += [run_decode(world, rank, dev, "70b", batch, 512, 256, 3.5, peer=peer) for batch in (1, 16)]
         extra["decode"] = dec
 
     if rank != 0:

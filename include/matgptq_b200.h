@@ -235,6 +235,7 @@ int matgptq_b200_dequantize(const uint32_t *packed, const void *scales, const vo
  *   rope_kv:     qkv[B,S,(H+2KV)*d] -> q_out[B,H,S,d] rotated (pairs 2i,2i+1); rotated k and v are
  *                written into the caches [B,KV,max_seq,d] at positions[s]; cos/sin are [max_seq,d/2] fp32
  *   silu_mul:    gate_up[rows,2*I] -> out[rows,I] = silu(gate) * up
+ *   argmax:      logits[rows,cols] (cols % 8 == 0) -> out[rows] int64: the first index of the row's maximum (greedy sampling)
  */
 int matgptq_b200_add_rmsnorm(void *x, const void *delta, const void *weight, void *h, int64_t rows, int64_t hidden,
                              float eps, uint32_t flags, void *stream);
@@ -242,6 +243,7 @@ int matgptq_b200_rope_kv(const void *qkv, const int64_t *positions, const float 
                          void *q_out, void *k_cache, void *v_cache, int64_t batch, int64_t seq, int64_t n_heads,
                          int64_t n_kv_heads, int64_t head_dim, int64_t max_seq, uint32_t flags, void *stream);
 int matgptq_b200_silu_mul(const void *gate_up, void *out, int64_t rows, int64_t intermediate, uint32_t flags, void *stream);
+int matgptq_b200_argmax(const void *logits, int64_t *out, int64_t rows, int64_t cols, uint32_t flags, void *stream);
 
 /*
  * Waits inside the kernels (on asynchronous copies) are bounded: a kernel that gives

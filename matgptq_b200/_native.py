@@ -48,6 +48,7 @@ SIGNATURES = {
     "matgptq_b200_matmul_static_scratch": (_c_int, [_c_i64, _c_i64, _c_i64, _c_i64, _c_i64, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_u32]),
     "matgptq_b200_add_rmsnorm": (_c_int, [_c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_i64, _c_i64, ctypes.c_float, _c_u32, _c_ptr]),
     "matgptq_b200_rope_kv": (_c_int, [_c_ptr] * 7 + [_c_i64] * 6 + [_c_u32, _c_ptr]),
+    "matgptq_b200_argmax": (_c_int, [_c_ptr, _c_ptr, _c_i64, _c_i64, _c_u32, _c_ptr]),
     "matgptq_b200_silu_mul": (_c_int, [_c_ptr, _c_ptr, _c_i64, _c_i64, _c_u32, _c_ptr]),
     "matgptq_b200_slice": (_c_int, [_c_ptr, _c_ptr, _c_i64, _c_int, _c_int, _c_ptr]),
     "matgptq_b200_pack_qweights": (_c_int, [_c_ptr, _c_ptr, _c_i64, _c_i64, _c_int, _c_int, _c_ptr]),

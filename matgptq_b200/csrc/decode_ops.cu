@@ -155,6 +155,59 @@ __global__ void silu_mul_kernel(const T *__restrict__ gu, T *__restrict__ out, l
   }
 }
 
+// Greedy sampling: index of the largest logit of every row (the first one on ties), one CTA per row.  Logits
+// [rows, cols] in the model dtype; `cols` a multiple of 8 and rows 16-byte aligned for the vector loads.
+template <typename T>
+__global__ void __launch_bounds__(1024, 1) argmax_kernel(const T *__restrict__ logits, long long *__restrict__ out, int cols) {
+  const T *row = logits + static_cast<long long>(blockIdx.x) * cols;
+  float best = -INFINITY;
+  int best_i = 0x7fffffff;
+  for (int c = threadIdx.x * 8; c < cols; c += blockDim.x * 8) {
+    const uint4 v = *reinterpret_cast<const uint4 *>(row + c);
+    const T *e = reinterpret_cast<const T *>(&v);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      const float f = to_f(e[k]);
+      if (f > best) {  // strictly greater: within a thread the columns ascend, so the first maximum stays
+        best = f;
+        best_i = c + k;
+      }
+    }
+  }
+  __shared__ float s_val[32];
+  __shared__ int s_idx[32];
+  auto better = [](float a, int ai, float b, int bi) { return a > b || (a == b && ai < bi); };
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) {
+    const float ov = __shfl_down_sync(0xffffffffu, best, off);
+    const int oi = __shfl_down_sync(0xffffffffu, best_i, off);
+    if (better(ov, oi, best, best_i)) {
+      best = ov;
+      best_i = oi;
+    }
+  }
+  if ((threadIdx.x & 31) == 0) {
+    s_val[threadIdx.x >> 5] = best;
+    s_idx[threadIdx.x >> 5] = best_i;
+  }
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    const int nw = blockDim.x >> 5;
+    best = threadIdx.x < nw ? s_val[threadIdx.x] : -INFINITY;
+    best_i = threadIdx.x < nw ? s_idx[threadIdx.x] : 0x7fffffff;
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) {
+      const float ov = __shfl_down_sync(0xffffffffu, best, off);
+      const int oi = __shfl_down_sync(0xffffffffu, best_i, off);
+      if (better(ov, oi, best, best_i)) {
+        best = ov;
+        best_i = oi;
+      }
+    }
+    if (threadIdx.x == 0) out[blockIdx.x] = best_i == 0x7fffffff ? 0 : best_i;
+  }
+}
+
 static unsigned grid_for(long long total, int threads) {
   long long blocks = (total + threads - 1) / threads;
   if (blocks > 148LL * 16) blocks = 148LL * 16;
@@ -215,6 +268,21 @@ int matgptq_b200_rope_kv(const void *qkv, const int64_t *positions, const float 
         static_cast<const __half *>(qkv), pos, cos_table, sin_table, static_cast<__half *>(q_out), static_cast<__half *>(k_cache),
         static_cast<__half *>(v_cache), static_cast<int>(batch), static_cast<int>(seq), static_cast<int>(n_heads),
         static_cast<int>(n_kv_heads), static_cast<int>(head_dim), static_cast<int>(max_seq));
+  return cudaGetLastError() == cudaSuccess ? MG_OK : MG_ERR_CUDA;
+}
+
+int matgptq_b200_argmax(const void *logits, int64_t *out, int64_t rows, int64_t cols, uint32_t flags, void *stream) {
+  if (!logits || !out || rows < 0 || cols <= 0 || cols % 8 != 0 || cols > (1 << 30)) return MG_ERR_BAD_ARG;
+  if (reinterpret_cast<uintptr_t>(logits) & 15u) return MG_ERR_ALIGNMENT;
+  if (rows == 0) return MG_OK;
+  cudaStream_t cs = static_cast<cudaStream_t>(stream);
+  static_assert(sizeof(long long) == sizeof(int64_t), "int64_t is long long here");
+  if (flags & MATGPTQ_B200_FLAG_BF16)
+    mg::argmax_kernel<__nv_bfloat16><<<static_cast<unsigned>(rows), 1024, 0, cs>>>(
+        static_cast<const __nv_bfloat16 *>(logits), reinterpret_cast<long long *>(out), static_cast<int>(cols));
+  else
+    mg::argmax_kernel<__half><<<static_cast<unsigned>(rows), 1024, 0, cs>>>(static_cast<const __half *>(logits),
+                                                                          reinterpret_cast<long long *>(out), static_cast<int>(cols));
   return cudaGetLastError() == cudaSuccess ? MG_OK : MG_ERR_CUDA;
 }
 

@@ -180,8 +180,9 @@ class PackedLlama:
             return self.peer_ar.matmul(x, packed, scales, rows, L.n_in, bits, L.group_size, flag)
         return self._all_reduce(self.linear(layer, which, x))
 
-    def forward(self, tokens: torch.Tensor, positions: torch.Tensor) -> torch.Tensor:
-        """tokens [B, S] int64, positions [S] int64 (device) -> logits of the last position [B, vocab] (fp32)."""
+    def forward(self, tokens: torch.Tensor, positions: torch.Tensor, fp32_logits: bool = True) -> torch.Tensor:
+        """tokens [B, S] int64, positions [S] int64 (device) -> logits of the last position [B, vocab]
+        (fp32, or the model dtype with ``fp32_logits=False``)."""
         B, S = tokens.shape
         d, H = self.shape.head_dim, self.shape.hidden
         lib = _native.load()
@@ -216,7 +217,9 @@ class PackedLlama:
             nxt = self.layers[li + 1]["ln1"] if li + 1 < len(self.layers) else self.final_norm
             add_norm(x, dn, nxt, h)
         last = h.view(B, S, H)[:, -1]
-        logits = F.linear(last, self.lm_head).float()
+        logits = F.linear(last, self.lm_head)
+        if fp32_logits:
+            logits = logits.float()
         if self.tp_size > 1:
             parts = [torch.empty_like(logits) for _ in range(self.tp_size)]
             dist.all_gather(parts, logits)
@@ -242,8 +245,14 @@ class PackedLlama:
         pos = torch.full((1,), P, dtype=torch.int64, device=self.dev)
         step_idx = torch.zeros(1, dtype=torch.int64, device=self.dev)
 
+        lib = _native.load()
+        flag = _native.FLAG_BF16 if self.dtype == torch.bfloat16 else 0
+        nxt = torch.empty(B, 1, dtype=torch.int64, device=self.dev)
+
         def step():
-            nxt = self.forward(tok, pos).argmax(-1, keepdim=True)
+            logits16 = self.forward(tok, pos, fp32_logits=False).contiguous()
+            _native.check(lib.matgptq_b200_argmax(logits16.data_ptr(), nxt.data_ptr(), B, logits16.shape[1], flag,
+                                                  torch.cuda.current_stream(self.dev).cuda_stream), "argmax")
             tok.copy_(nxt)
             pos.add_(1)
             step_idx.add_(1)

@@ -196,3 +196,25 @@ def test_decode_helper_kernels_match_torch(cuda, dtype):
     ref = F.silu(gu[:, :inter].float()).to(dtype) * gu[:, inter:]
     assert (out.float() - ref.float()).abs().max() <= 4 * torch.finfo(dtype).eps * ref.float().abs().max()
     assert lib.matgptq_b200_add_rmsnorm(None, None, w.data_ptr(), h.data_ptr(), 1, hidden, eps, flag, stream) != 0
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("rows,cols", [(1, 128256), (3, 4096), (8, 512), (2, 8)])
+def test_argmax_kernel_matches_torch(cuda, dtype, rows, cols):
+    """Greedy sampling helper: the first index of each row's maximum, ties and -inf included."""
+    from matgptq_b200 import _native
+    lib = _native.load()
+    g = torch.Generator(device=cuda).manual_seed(rows * cols)
+    logits = torch.randn(rows, cols, generator=g, device=cuda).to(dtype)
+    logits[0, cols // 2] = logits[0].max()       # a tie: the first of the two equal maxima wins
+    if rows > 1:
+        logits[1] = float("-inf")                # nothing is larger than anything: index 0
+        logits[1, cols - 1] = -3.0
+    out = torch.full((rows,), -1, dtype=torch.int64, device=cuda)
+    flag = _native.FLAG_BF16 if dtype == torch.bfloat16 else 0
+    _native.check(lib.matgptq_b200_argmax(logits.data_ptr(), out.data_ptr(), rows, cols, flag,
+                                          torch.cuda.current_stream(cuda).cuda_stream), "argmax")
+    want = torch.stack([(row == row.max()).nonzero()[0, 0] for row in logits.float()])
+    assert torch.equal(out, want)
+    assert lib.matgptq_b200_argmax(logits.data_ptr(), out.data_ptr(), rows, 12, flag, None) == 1  # cols % 8 != 0
