@@ -77,13 +77,14 @@ int matgptq_b200_matmul_tuned(int64_t bitwidth, int64_t group_size, int64_t n_ou
                               int warps_per_cta, int split_k);
 
 /*
- * The same product with caller-provided scratch memory.  Batches of 32 rows and more run
- * on the tensor cores (tcgen05); for shapes with few 128-row tiles that path splits K over
+ * The same product with caller-provided scratch memory.  Batches of more than 16 rows run
+ * on the tensor cores (tcgen05) (from 40 rows for layers with fewer than 2048 out-features, which
+ * the GEMV serves faster until then); for shapes with few 128-row tiles that path splits K over
  * several CTAs and parks fp32 partial sums in scratch: matgptq_b200_matmul_workspace_bytes(...)
  * gives the size (16-byte aligned; contents may be anything before the call and are undefined
  * after it; one buffer per stream in flight).  Without scratch (workspace NULL, or
  * matgptq_b200_matmul) K is not split.
- *   path: 0 = choose by batch size (cluster GEMV below 32 rows, tensor cores from 32),
+ *   path: 0 = choose by batch size and out-features as above,
  *         1 = cluster GEMV, 2 = tensor-core path (any batch size)
  *   split_k: 0 = choose; otherwise the number of CTAs along K (tensor-core path: needs
  *            split_k*M*N*4 bytes of scratch)

@@ -45,8 +45,19 @@ const char *matgptq_b200_strerror(int status) {
   }
 }
 
-// Batches from this size on take the tensor-core path (tcgen05), smaller ones the GEMV family.
+// Batches from this size on always take the tensor-core path (tcgen05); the fused and grouped small-batch
+// entry points serve batches below it.
 static const int64_t kTensorCoreMinBatch = 32;
+
+// Automatic choice between the GEMV family and the tensor-core path.  The GEMV handles 16 activation rows per
+// pass, so from 17 rows on it reads the weights twice (from L2) and doubles its tensor work; measured on B200
+// (bf16, group 128, cold L2): q/o 24 rows 14.2 us GEMV against 11.4 us tensor cores, down 32.5 against 24.4,
+// gate/up level; only layers with few row tiles (k/v, N = 1024: 6.6 against 8.3 us at 32 rows, 11.3 against 9.0
+// at 48) are better off on the GEMV up to three passes.
+static bool uses_tensor_cores(int64_t n_out, int64_t batch) {
+  if (n_out >= 2048) return batch > 16;
+  return batch >= 40;
+}
 
 static int sm_count_of_current_device(int *out) {
   int dev = 0;
@@ -69,7 +80,7 @@ static int matmul_impl(int64_t bitwidth, int64_t group_size, int64_t n_out, int6
   cudaStream_t cs = static_cast<cudaStream_t>(stream);
   const bool bf16 = (flags & MATGPTQ_B200_FLAG_BF16) != 0;
   const bool pdl = (flags & MATGPTQ_B200_FLAG_PDL) != 0;
-  const bool tensor_core = path == 2 || (path == 0 && batch >= kTensorCoreMinBatch);
+  const bool tensor_core = path == 2 || (path == 0 && uses_tensor_cores(n_out, batch));
   int r;
   if (z) {
     // zero points: every batch size runs on the GEMV family (more than 16 rows in passes of 16); the tensor-core
@@ -225,7 +236,7 @@ int64_t matgptq_b200_matmul_workspace_bytes(int64_t n_out, int64_t n_in, int64_t
   if (n_out <= 0 || n_in <= 0 || batch <= 0) return 0;
   int sms = 0;
   if (sm_count_of_current_device(&sms) != MG_OK) sms = 148;
-  if (batch < kTensorCoreMinBatch) return 0;
+  if (!uses_tensor_cores(n_out, batch)) return 0;
   return mg::gemm_tc_workspace_bytes(static_cast<int>(n_out), static_cast<int>(n_in), static_cast<int>(batch), sms);
 }
 

@@ -391,7 +391,7 @@ def matmul_matgptq_raw(x: torch.Tensor, packed: torch.Tensor, scales: torch.Tens
             if path == 2 and split_k > 1:
                 need = split_k * batch * n_out * 4
             elif path == 2:
-                need = _lib.matgptq_b200_matmul_workspace_bytes(n_out, n_in, max(batch, 32))
+                need = _lib.matgptq_b200_matmul_workspace_bytes(n_out, n_in, max(batch, 64))
             else:
                 need = _lib.matgptq_b200_matmul_workspace_bytes(n_out, n_in, batch)
             if need > 0:
