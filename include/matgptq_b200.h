@@ -231,7 +231,8 @@ int matgptq_b200_dequantize(const uint32_t *packed, const void *scales, const vo
 /*
  * Helpers of the decode harness (matgptq_b200/decode.py); the reference leaves these steps to
  * vLLM / transformers and has no counterpart.  All tensors are device, contiguous, fp16 or bf16
- * (FLAG_BF16); arithmetic is fp32.
+ * (FLAG_BF16); arithmetic is fp32.  With FLAG_PDL they are launched with programmatic dependent launch as
+ * well: each lets the kernel behind it start its prologue at once and waits for the kernel before it.
  *   add_rmsnorm: x[rows,hidden] += delta (when delta != NULL); h = rmsnorm(x) * weight
  *   rope_kv:     qkv[B,S,(H+2KV)*d] -> q_out[B,H,S,d] rotated (pairs 2i,2i+1); rotated k and v are
  *                written into the caches [B,KV,max_seq,d] at positions[s]; cos/sin are [max_seq,d/2] fp32

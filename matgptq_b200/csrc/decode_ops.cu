@@ -22,9 +22,34 @@ template <> __device__ __forceinline__ __half from_f<__half>(float v) { return _
 template <> __device__ __forceinline__ __nv_bfloat16 from_f<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
 
 // x[row] += delta[row] (when delta != null), then h[row] = rmsnorm(x[row]) * weight.  One CTA per row.
+// Programmatic dependent launch: let the next kernel of the stream start its prologue now (the packed products
+// prefetch their weights there), then wait until the previous kernel's results are complete and visible.  Both
+// are no-ops for a kernel that was launched without the attribute and has no dependents.
+__device__ __forceinline__ void pdl_prologue() {
+  asm volatile("griddepcontrol.launch_dependents;");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+
+template <typename Kernel, typename... Args>
+static int launch_helper(Kernel kernel, unsigned grid, unsigned block, cudaStream_t stream, bool pdl, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid, 1, 1);
+  cfg.blockDim = dim3(block, 1, 1);
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  if (pdl) {
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+  }
+  return cudaLaunchKernelEx(&cfg, kernel, args...) == cudaSuccess ? MG_OK : MG_ERR_CUDA;
+}
+
 template <typename T>
 __global__ void __launch_bounds__(256) add_rmsnorm_kernel(T *__restrict__ x, const T *__restrict__ delta, const T *__restrict__ weight,
                                                           T *__restrict__ h, int hidden, float eps) {
+  pdl_prologue();
   __shared__ float red[8];
   T *xr = x + static_cast<size_t>(blockIdx.x) * hidden;
   const T *dr = delta ? delta + static_cast<size_t>(blockIdx.x) * hidden : nullptr;
@@ -54,6 +79,7 @@ template <typename T>
 __global__ void __launch_bounds__(kNormThreads) add_rmsnorm_vec_kernel(T *__restrict__ x, const T *__restrict__ delta,
                                                                        const T *__restrict__ weight, T *__restrict__ h, int hidden,
                                                                        float eps) {
+  pdl_prologue();
   __shared__ float red[kNormThreads / 32];
   const int nvec = hidden >> 3;
   uint4 *xr = reinterpret_cast<uint4 *>(x + static_cast<size_t>(blockIdx.x) * hidden);
@@ -114,6 +140,7 @@ template <typename T>
 __global__ void rope_kv_kernel(const T *__restrict__ qkv, const long long *__restrict__ positions, const float *__restrict__ cos_t,
                                const float *__restrict__ sin_t, T *__restrict__ q_out, T *__restrict__ k_cache, T *__restrict__ v_cache,
                                int B, int S, int H, int KV, int d, int max_seq) {
+  pdl_prologue();
   const int heads = H + 2 * KV, half = d / 2;
   const long long total = static_cast<long long>(B) * S * heads * half;
   for (long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; idx < total;
@@ -144,6 +171,7 @@ __global__ void rope_kv_kernel(const T *__restrict__ qkv, const long long *__res
 // gu [rows, 2*inter] -> out [rows, inter] = silu(gate) * up, both factors rounded to the model dtype first
 template <typename T>
 __global__ void silu_mul_kernel(const T *__restrict__ gu, T *__restrict__ out, long long rows, int inter) {
+  pdl_prologue();
   const long long total = rows * inter;
   for (long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; idx < total;
        idx += static_cast<long long>(gridDim.x) * blockDim.x) {
@@ -159,6 +187,7 @@ __global__ void silu_mul_kernel(const T *__restrict__ gu, T *__restrict__ out, l
 // [rows, cols] in the model dtype; `cols` a multiple of 8 and rows 16-byte aligned for the vector loads.
 template <typename T>
 __global__ void __launch_bounds__(1024, 1) argmax_kernel(const T *__restrict__ logits, long long *__restrict__ out, int cols) {
+  pdl_prologue();
   const T *row = logits + static_cast<long long>(blockIdx.x) * cols;
   float best = -INFINITY;
   int best_i = 0x7fffffff;
@@ -229,22 +258,23 @@ int matgptq_b200_add_rmsnorm(void *x, const void *delta, const void *weight, voi
                     reinterpret_cast<uintptr_t>(h)) % 16 == 0;
   const unsigned grid = static_cast<unsigned>(rows);
   const int hd = static_cast<int>(hidden);
+  const bool pdl = (flags & MATGPTQ_B200_FLAG_PDL) != 0;
   if (flags & MATGPTQ_B200_FLAG_BF16) {
     using T = __nv_bfloat16;
     if (vec)
-      mg::add_rmsnorm_vec_kernel<T><<<grid, mg::kNormThreads, 0, cs>>>(static_cast<T *>(x), static_cast<const T *>(delta),
-                                                                      static_cast<const T *>(weight), static_cast<T *>(h), hd, eps);
+      return mg::launch_helper(mg::add_rmsnorm_vec_kernel<T>, grid, mg::kNormThreads, cs, pdl, static_cast<T *>(x),
+                               static_cast<const T *>(delta), static_cast<const T *>(weight), static_cast<T *>(h), hd, eps);
     else
-      mg::add_rmsnorm_kernel<T><<<grid, 256, 0, cs>>>(static_cast<T *>(x), static_cast<const T *>(delta),
-                                                     static_cast<const T *>(weight), static_cast<T *>(h), hd, eps);
+      return mg::launch_helper(mg::add_rmsnorm_kernel<T>, grid, 256, cs, pdl, static_cast<T *>(x), static_cast<const T *>(delta),
+                               static_cast<const T *>(weight), static_cast<T *>(h), hd, eps);
   } else {
     using T = __half;
     if (vec)
-      mg::add_rmsnorm_vec_kernel<T><<<grid, mg::kNormThreads, 0, cs>>>(static_cast<T *>(x), static_cast<const T *>(delta),
-                                                                      static_cast<const T *>(weight), static_cast<T *>(h), hd, eps);
+      return mg::launch_helper(mg::add_rmsnorm_vec_kernel<T>, grid, mg::kNormThreads, cs, pdl, static_cast<T *>(x),
+                               static_cast<const T *>(delta), static_cast<const T *>(weight), static_cast<T *>(h), hd, eps);
     else
-      mg::add_rmsnorm_kernel<T><<<grid, 256, 0, cs>>>(static_cast<T *>(x), static_cast<const T *>(delta),
-                                                     static_cast<const T *>(weight), static_cast<T *>(h), hd, eps);
+      return mg::launch_helper(mg::add_rmsnorm_kernel<T>, grid, 256, cs, pdl, static_cast<T *>(x), static_cast<const T *>(delta),
+                               static_cast<const T *>(weight), static_cast<T *>(h), hd, eps);
   }
   return cudaGetLastError() == cudaSuccess ? MG_OK : MG_ERR_CUDA;
 }
@@ -259,12 +289,12 @@ int matgptq_b200_rope_kv(const void *qkv, const int64_t *positions, const float 
   const unsigned grid = mg::grid_for(total, 256);
   const long long *pos = reinterpret_cast<const long long *>(positions);
   if (flags & MATGPTQ_B200_FLAG_BF16)
-    mg::rope_kv_kernel<__nv_bfloat16><<<grid, 256, 0, cs>>>(
+    return mg::launch_helper(mg::rope_kv_kernel<__nv_bfloat16>, grid, 256, cs, (flags & MATGPTQ_B200_FLAG_PDL) != 0,
         static_cast<const __nv_bfloat16 *>(qkv), pos, cos_table, sin_table, static_cast<__nv_bfloat16 *>(q_out),
         static_cast<__nv_bfloat16 *>(k_cache), static_cast<__nv_bfloat16 *>(v_cache), static_cast<int>(batch), static_cast<int>(seq),
         static_cast<int>(n_heads), static_cast<int>(n_kv_heads), static_cast<int>(head_dim), static_cast<int>(max_seq));
   else
-    mg::rope_kv_kernel<__half><<<grid, 256, 0, cs>>>(
+    return mg::launch_helper(mg::rope_kv_kernel<__half>, grid, 256, cs, (flags & MATGPTQ_B200_FLAG_PDL) != 0,
         static_cast<const __half *>(qkv), pos, cos_table, sin_table, static_cast<__half *>(q_out), static_cast<__half *>(k_cache),
         static_cast<__half *>(v_cache), static_cast<int>(batch), static_cast<int>(seq), static_cast<int>(n_heads),
         static_cast<int>(n_kv_heads), static_cast<int>(head_dim), static_cast<int>(max_seq));
@@ -278,11 +308,11 @@ int matgptq_b200_argmax(const void *logits, int64_t *out, int64_t rows, int64_t 
   cudaStream_t cs = static_cast<cudaStream_t>(stream);
   static_assert(sizeof(long long) == sizeof(int64_t), "int64_t is long long here");
   if (flags & MATGPTQ_B200_FLAG_BF16)
-    mg::argmax_kernel<__nv_bfloat16><<<static_cast<unsigned>(rows), 1024, 0, cs>>>(
+    return mg::launch_helper(mg::argmax_kernel<__nv_bfloat16>, static_cast<unsigned>(rows), 1024, cs, (flags & MATGPTQ_B200_FLAG_PDL) != 0,
         static_cast<const __nv_bfloat16 *>(logits), reinterpret_cast<long long *>(out), static_cast<int>(cols));
   else
-    mg::argmax_kernel<__half><<<static_cast<unsigned>(rows), 1024, 0, cs>>>(static_cast<const __half *>(logits),
-                                                                          reinterpret_cast<long long *>(out), static_cast<int>(cols));
+    return mg::launch_helper(mg::argmax_kernel<__half>, static_cast<unsigned>(rows), 1024, cs, (flags & MATGPTQ_B200_FLAG_PDL) != 0,
+                             static_cast<const __half *>(logits), reinterpret_cast<long long *>(out), static_cast<int>(cols));
   return cudaGetLastError() == cudaSuccess ? MG_OK : MG_ERR_CUDA;
 }
 
@@ -292,11 +322,13 @@ int matgptq_b200_silu_mul(const void *gate_up, void *out, int64_t rows, int64_t 
   cudaStream_t cs = static_cast<cudaStream_t>(stream);
   const unsigned grid = mg::grid_for(rows * intermediate, 256);
   if (flags & MATGPTQ_B200_FLAG_BF16)
-    mg::silu_mul_kernel<__nv_bfloat16><<<grid, 256, 0, cs>>>(static_cast<const __nv_bfloat16 *>(gate_up),
-                                                            static_cast<__nv_bfloat16 *>(out), rows, static_cast<int>(intermediate));
+    return mg::launch_helper(mg::silu_mul_kernel<__nv_bfloat16>, grid, 256, cs, (flags & MATGPTQ_B200_FLAG_PDL) != 0,
+                             static_cast<const __nv_bfloat16 *>(gate_up), static_cast<__nv_bfloat16 *>(out),
+                             static_cast<long long>(rows), static_cast<int>(intermediate));
   else
-    mg::silu_mul_kernel<__half><<<grid, 256, 0, cs>>>(static_cast<const __half *>(gate_up), static_cast<__half *>(out), rows,
-                                                     static_cast<int>(intermediate));
+    return mg::launch_helper(mg::silu_mul_kernel<__half>, grid, 256, cs, (flags & MATGPTQ_B200_FLAG_PDL) != 0,
+                             static_cast<const __half *>(gate_up), static_cast<__half *>(out), static_cast<long long>(rows),
+                             static_cast<int>(intermediate));
   return cudaGetLastError() == cudaSuccess ? MG_OK : MG_ERR_CUDA;
 }
 

@@ -186,7 +186,9 @@ class PackedLlama:
         B, S = tokens.shape
         d, H = self.shape.head_dim, self.shape.hidden
         lib = _native.load()
-        flag = _native.FLAG_BF16 if self.dtype == torch.bfloat16 else 0
+        # the helper kernels take part in programmatic dependent launch: the product behind each of them starts
+        # prefetching its weights while the helper still runs
+        flag = (_native.FLAG_BF16 if self.dtype == torch.bfloat16 else 0) | (_native.FLAG_PDL if self.pdl else 0)
         stream = torch.cuda.current_stream(self.dev).cuda_stream
         rows = B * S
 
@@ -246,7 +248,7 @@ class PackedLlama:
         step_idx = torch.zeros(1, dtype=torch.int64, device=self.dev)
 
         lib = _native.load()
-        flag = _native.FLAG_BF16 if self.dtype == torch.bfloat16 else 0
+        flag = (_native.FLAG_BF16 if self.dtype == torch.bfloat16 else 0) | (_native.FLAG_PDL if self.pdl else 0)
         nxt = torch.empty(B, 1, dtype=torch.int64, device=self.dev)
 
         def step():
