@@ -42,12 +42,15 @@ class MatGPTQLinear(torch.nn.Module):
 
     @classmethod
     def from_master(cls, qweight_master: torch.Tensor, scales: torch.Tensor, master_bitwidth: int, bitwidth: int,
-                    group_size: int) -> "MatGPTQLinear":
+                    group_size: int, keep_master: bool = False) -> "MatGPTQLinear":
         """Addition: build the layer from UNSLICED master codes; the MSB slicing of
         ``matryoshka_slice`` (``src/quant_utils_matgpqt.py:9-17``) is fused into the GPU packer instead of
-        being a separate pass (``inference_demo_transformers.py:30-39``)."""
+        being a separate pass (``inference_demo_transformers.py:30-39``).  With ``keep_master`` the uint8 master
+        codes stay resident on the GPU and ``set_bitwidth`` re-slices from them at run time."""
         self = cls.__new__(cls)
         torch.nn.Module.__init__(self)
+        self.master_bitwidth = master_bitwidth
+        self.register_buffer("master_qweight", qweight_master.contiguous() if keep_master else None, persistent=False)
         self.n_out_features, self.n_in_features = qweight_master.shape
         self.bitwidth, self.group_size = bitwidth, group_size
         self.flag = MatGTPQ_FeatureFlags.ASYNC + MatGTPQ_FeatureFlags.IS_BF16 * (scales.dtype == torch.bfloat16)
@@ -61,6 +64,22 @@ class MatGPTQLinear(torch.nn.Module):
                 scales.contiguous(), self.n_out_features, self.n_in_features, group_size),
             requires_grad=False)
         return self
+
+    @torch.no_grad()
+    def set_bitwidth(self, bitwidth: int) -> None:
+        """Addition: serve this layer at another bitwidth from the resident master codes (one GPU pass of the
+        fused slice + pack kernel; the scales do not depend on the bitwidth).  The reference switches bitwidth by
+        re-running slice and host-side pack for the whole model (``vllm_matgptq.py:150-178``)."""
+        if getattr(self, "master_qweight", None) is None:
+            raise RuntimeError("set_bitwidth needs the master codes: build the layer with from_master(..., keep_master=True)")
+        if bitwidth == self.bitwidth:
+            return
+        self.matgptq_qweight = torch.nn.Parameter(
+            torch.ops.matgptq_cuda.slice_pack_matgptq_qweights(
+                self.master_qweight, self.n_out_features, self.n_in_features, self.master_bitwidth, bitwidth,
+                self.group_size, self.flag),
+            requires_grad=False)
+        self.bitwidth = bitwidth
 
     @torch.no_grad()
     def forward(self, x: torch.Tensor) -> torch.Tensor:

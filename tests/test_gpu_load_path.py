@@ -111,3 +111,22 @@ def test_a_wait_that_runs_out_is_reported_and_the_device_stays_usable(lib, cuda,
     assert lib.matgptq_b200_slice(x.data_ptr(), out.data_ptr(), 256, 8, 4, torch.cuda.current_stream().cuda_stream) == 0
     torch.cuda.synchronize()
     assert int(out.max()) == 15
+
+
+def test_runtime_bitwidth_switch_from_resident_master(cuda):
+    """One resident copy of the 8-bit master codes serves every bitwidth: set_bitwidth re-slices and re-packs on
+    the GPU, and after every switch the layer computes what the oracle computes at that bitwidth."""
+    from matgptq_b200 import synth
+    from matgptq_b200.matgptq_linear import MatGPTQLinear
+    n_out, n_in = 512, 1024
+    layer = synth.make_layer(n_out, n_in, 128, seed=2, sym=True, dtype=torch.float16, device=cuda)
+    lin = MatGPTQLinear.from_master(layer.qweight, layer.scales, 8, 8, 128, keep_master=True)
+    x = synth.make_activations(5, n_in, seed=3, dtype=torch.float16, device=cuda)
+    for b in (8, 2, 4, 3, 6, 8):
+        lin.set_bitwidth(b)
+        assert lin.bitwidth == b and lin.matgptq_qweight.numel() == b * n_out * n_in // 32
+        w_ref = oracle.dequantize_weight(layer.qweight.cpu(), layer.scales.cpu(), layer.zeros.cpu(), 8, b)
+        assert oracle.rel_err(lin(x).cpu(), oracle.linear_fp32_accumulate(x.cpu(), w_ref)) <= 1e-2
+    plain = MatGPTQLinear.from_master(layer.qweight, layer.scales, 8, 4, 128)
+    with pytest.raises(RuntimeError, match="keep_master"):
+        plain.set_bitwidth(2)
