@@ -749,17 +749,20 @@ def single_cell_main(args) -> None:
     b, m = int(b), int(m)
     k, n = synth.LLAMA3_8B_SHAPES[name]
     dev = torch.device("cuda", 0)
-    layer = synth.make_layer(n, k, GROUP, seed=1, sym=True, dtype=torch.float16, device=dev)
+    dtype = torch.bfloat16 if args.bf16 else torch.float16
+    layer = synth.make_layer(n, k, GROUP, seed=1, sym=True, dtype=dtype, device=dev)
     scales_r = torch.ops.matgptq_cuda.reorder_matgptq_scales(layer.scales, n, k, GROUP)
     packed = torch.ops.matgptq_cuda.slice_pack_matgptq_qweights(layer.qweight, n, k, 8, b, GROUP, 1)
     copies = max(2, min(32, -(-256 * 1024 * 1024 // (packed.numel() * 4))))
     packs = [packed] + [packed.clone() for _ in range(copies - 1)]
-    x = synth.make_activations(m, k, seed=m, dtype=torch.float16, device=dev)
-    y = torch.empty(m, n, dtype=torch.float16, device=dev)
-    flags = _native.FLAG_ASYNC | (_native.FLAG_PDL if not args.no_pdl else 0)
+    x = synth.make_activations(m, k, seed=m, dtype=dtype, device=dev)
+    y = torch.empty(m, n, dtype=dtype, device=dev)
+    flags = _native.FLAG_ASYNC | (_native.FLAG_PDL if not args.no_pdl else 0) | (_native.FLAG_BF16 if args.bf16 else 0)
+    need = ops._lib.matgptq_b200_matmul_workspace_bytes(n, k, m)
+    ws = torch.empty(max(need, 16), dtype=torch.uint8, device=dev)
     torch.cuda.synchronize()
     for i in range(args.launches):
-        ops.matmul_matgptq_raw(x, packs[i % copies], scales_r, n, k, b, GROUP, flags, out=y)
+        ops.matmul_matgptq_raw(x, packs[i % copies], scales_r, n, k, b, GROUP, flags, out=y, workspace=ws if need else None)
     torch.cuda.synchronize()
     print(json.dumps({"cell": args.cell, "launches": args.launches, "copies": copies,
                       "algorithmic_bytes": synth.algorithmic_bytes(n, k, m, b, GROUP)}))
@@ -794,6 +797,7 @@ def main() -> None:
     ap.add_argument("--cell", type=str, default=None,
                     help="shape:b:m, e.g. q_o:4:1 - only launch this cell (--launches times) and exit")
     ap.add_argument("--launches", type=int, default=8)
+    ap.add_argument("--bf16", action="store_true", help="with --cell: bfloat16 activations, scales and output")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=3)

@@ -32,10 +32,12 @@ extern "C" {
 #define MATGPTQ_B200_ERR_SCRATCH_UNAVAILABLE 6 /* the built-in scratch array could not be set up on this device */
 
 /* feature flags: bits 0 and 1 are the reference's (csrc/include/common.cuh:78-86,
- * matgptq_cuda/matgptq_linear.py:6-9); bit 2 is an addition. */
+ * matgptq_cuda/matgptq_linear.py:6-9); bits 2 and 3 are additions. */
 #define MATGPTQ_B200_FLAG_ASYNC 1 /* do not synchronise the device after the launch */
 #define MATGPTQ_B200_FLAG_BF16 2  /* activations, scales and output are bfloat16 (else float16) */
 #define MATGPTQ_B200_FLAG_PDL 4   /* launch with programmatic dependent launch: weight prefetch overlaps the previous kernel */
+#define MATGPTQ_B200_FLAG_SCRATCH_REDUCE 8 /* tensor-core path: add the sums of a split K through scratch memory and a second
+                                            * kernel instead of inside a thread-block cluster (needs the scratch) */
 
 /* Library version (major*10000 + minor*100 + patch). */
 int matgptq_b200_version(void);
@@ -77,17 +79,20 @@ int matgptq_b200_matmul_tuned(int64_t bitwidth, int64_t group_size, int64_t n_ou
                               int warps_per_cta, int split_k);
 
 /*
- * The same product with caller-provided scratch memory.  Batches of more than 16 rows run
+ * The same product with optional scratch memory and a forced path.  Batches of more than 16 rows run
  * on the tensor cores (tcgen05) (from 40 rows for layers with fewer than 2048 out-features, which
  * the GEMV serves faster until then); for shapes with few 128-row tiles that path splits K over
- * several CTAs and parks fp32 partial sums in scratch: matgptq_b200_matmul_workspace_bytes(...)
- * gives the size (16-byte aligned; contents may be anything before the call and are undefined
- * after it; one buffer per stream in flight).  Without scratch (workspace NULL, or
- * matgptq_b200_matmul) K is not split.
+ * up to eight CTAs, which form a thread-block cluster and add their fp32 sums through distributed
+ * shared memory, so that no scratch is needed.  Scratch of matgptq_b200_matmul_workspace_bytes(...)
+ * bytes (16-byte aligned; contents may be anything before the call and are undefined after it; one
+ * buffer per stream in flight) is used in two cases only: with FLAG_SCRATCH_REDUCE the sums go through
+ * it and a second kernel, and when the device cannot place the cluster (a partitioned GPU) the launch
+ * falls back to that form if the scratch is there (else MATGPTQ_B200_ERR_CUDA).  Both forms add in the
+ * order of the K ranges and give identical bits.
  *   path: 0 = choose by batch size and out-features as above,
  *         1 = cluster GEMV, 2 = tensor-core path (any batch size)
- *   split_k: 0 = choose; otherwise the number of CTAs along K (tensor-core path: needs
- *            split_k*M*N*4 bytes of scratch)
+ *   split_k: 0 = choose; otherwise the number of CTAs along K (tensor-core path: at most 8; with
+ *            FLAG_SCRATCH_REDUCE it needs split_k*M*N*4 bytes of scratch)
  * The reference has one kernel pair for all batch sizes and no scratch
  * (csrc/matgptq_gemm.cu:955-964); this entry has no counterpart there.
  */
@@ -159,14 +164,15 @@ int64_t matgptq_b200_matmul_workspace_bytes(int64_t n_out, int64_t n_in, int64_t
 /*
  * matgptq_b200_matmul_ws for callers that cannot allocate: hosts whose memory pool already
  * owns the whole device, plugins without access to their host's allocator, loops in which
- * cudaMalloc is forbidden because it synchronises the device.  The split-K scratch is a fixed
- * array of MATGPTQ_B200_STATIC_SCRATCH_BYTES inside the library image; once set up on a GPU it
- * occupies that much of its memory until the process exits.  This entry point has no
+ * cudaMalloc is forbidden because it synchronises the device.  The scratch of a K split (used as
+ * matgptq_b200_matmul_ws describes: with FLAG_SCRATCH_REDUCE, or when the device cannot place the
+ * cluster) is a fixed array of MATGPTQ_B200_STATIC_SCRATCH_BYTES inside the library image; once set up
+ * on a GPU it occupies that much of its memory until the process exits.  This entry point has no
  * counterpart in the reference.
  *   - It calls no cudaMalloc, cudaFree or any other allocating routine.
- *   - Shapes whose scratch need (matgptq_b200_matmul_workspace_bytes) exceeds the array return
- *     MATGPTQ_B200_ERR_SCRATCH_TOO_SMALL and launch nothing.
- *   - The first call on a device that needs scratch resolves the array's device address
+ *   - Shapes whose scratch need (matgptq_b200_matmul_workspace_bytes) exceeds the array run without
+ *     scratch; with FLAG_SCRATCH_REDUCE they return MATGPTQ_B200_ERR_SCRATCH_TOO_SMALL and launch nothing.
+ *   - The first call on a device for a shape that splits K resolves the array's device address
  *     (cudaGetSymbolAddress, with that device current) and remembers it.  The CUDA runtime loads
  *     device code lazily, so it is THIS first call that brings the array into the device's memory:
  *     the driver takes the MATGPTQ_B200_STATIC_SCRATCH_BYTES then, not when the library is loaded.

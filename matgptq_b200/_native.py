@@ -16,6 +16,7 @@ OK = 0
 FLAG_ASYNC = 1
 FLAG_BF16 = 2
 FLAG_PDL = 4
+FLAG_SCRATCH_REDUCE = 8
 
 _c_i64 = ctypes.c_int64
 _c_int = ctypes.c_int

@@ -91,7 +91,7 @@ static int matmul_impl(int64_t bitwidth, int64_t group_size, int64_t n_out, int6
   } else if (tensor_core) {
     r = mg::gemm_tc_launch(static_cast<int>(bitwidth), static_cast<int>(group_size), static_cast<int>(n_out),
                            static_cast<int>(n_in), static_cast<int>(batch), w, s, x, y, workspace, workspace_bytes, bf16,
-                           pdl, split_k, cs);
+                           pdl, split_k, cs, 0, (flags & MATGPTQ_B200_FLAG_SCRATCH_REDUCE) != 0);
   } else {
     r = mg::gemv_launch(static_cast<int>(bitwidth), static_cast<int>(group_size), static_cast<int>(n_out),
                         static_cast<int>(n_in), static_cast<int>(batch), w, s, nullptr, x, y, bf16, pdl, warps_per_cta, split_k, cs);
@@ -166,7 +166,7 @@ int matgptq_b200_matmul_grouped(const matgptq_b200_segment *segments, int n_segm
         r = mg::gemm_tc_launch(static_cast<int>(segments[i].bitwidth), static_cast<int>(group_size),
                                static_cast<int>(segments[i].n_out), static_cast<int>(n_in), static_cast<int>(batch),
                                segments[i].w, segments[i].s, x, yi, workspace, workspace_bytes, bf16, pdl, 0, cs,
-                               static_cast<int>(total));
+                               static_cast<int>(total), (flags & MATGPTQ_B200_FLAG_SCRATCH_REDUCE) != 0);
       else
         r = mg::gemv_launch(static_cast<int>(segments[i].bitwidth), static_cast<int>(group_size),
                             static_cast<int>(segments[i].n_out), static_cast<int>(n_in), static_cast<int>(batch),

@@ -201,9 +201,74 @@ template <int B, int P_OFF> __device__ __forceinline__ uint32_t dense_int_at(uin
   return h2_bits(__hfma2(bits_h2(x), bits_h2(mul), bits_h2(add)));
 }
 
+// Bit pattern of a bfloat16 value that is exactly representable and normal, duplicated into both halves.
+constexpr uint32_t bf162_const(float v) {
+  uint32_t sign = 0;
+  if (v < 0.0f) {
+    sign = 0x8000u;
+    v = -v;
+  }
+  int e = 0;
+  while (v >= 2.0f) {
+    v *= 0.5f;
+    ++e;
+  }
+  while (v < 1.0f) {
+    v *= 2.0f;
+    --e;
+  }
+  const uint32_t mant = static_cast<uint32_t>((v - 1.0f) * 128.0f);
+  const uint32_t h = sign | (static_cast<uint32_t>(e + 127) << 7) | mant;
+  return h | (h << 16);
+}
+
+// (128 + c*2^P) -> (c - Z) * DensePre<B> for both bfloat16 halves, one fused multiply-add with exact operands
+template <int B, int P_OFF> __device__ __forceinline__ uint32_t dense_int_bf16_at(uint32_t x) {
+  constexpr float pre = static_cast<float>(DensePre<B>::value);
+  constexpr float inv = pre / static_cast<float>(1 << P_OFF);
+  constexpr uint32_t mul = bf162_const(inv);
+  constexpr uint32_t add = bf162_const(-(128.0f * inv + static_cast<float>(BlockTraits<B>::ZERO) * pre));
+  const __nv_bfloat162 r = __hfma2(*reinterpret_cast<const __nv_bfloat162 *>(&x), *reinterpret_cast<const __nv_bfloat162 *>(&mul),
+                                   *reinterpret_cast<const __nv_bfloat162 *>(&add));
+  return *reinterpret_cast<const uint32_t *>(&r);
+}
+
+// Pair P of a lane as bfloat16 integers (code - Z) * DensePre<B>, WITHOUT the detour over fp16 (magic, fma, two
+// conversions): the field is isolated inside the 7 mantissa bits of bfloat16 with the exponent of 128 OR-ed in by
+// the same LOP3 (value 128 + code * 2^p), and one bfloat16 fma makes the integer.  Needs code * 2^p < 128, i.e.
+// the field shifted down to bit 0 first where it sits higher (every 4-bit field but the lowest, the third offset of
+// 3-bit codes); 8-bit codes do not fit 7 mantissa bits and keep the fp16 route.
+template <int B> __device__ __forceinline__ uint32_t dense_int_bf16(const uint32_t (&w)[2 * B], int P) {
+  static_assert(B != 8, "8-bit codes need 8 mantissa bits");
+  constexpr uint32_t kMagicBf = 0x43004300u;  // bfloat162(128, 128)
+  const int i = P >> 2, r = P & 3;
+  if constexpr (B == 4) {
+    const uint32_t W = w[4 * (i >> 2) + r] >> (4 * (i & 3));
+    return dense_int_bf16_at<4, 0>(lop3_and_or(W, 0x000F000Fu, kMagicBf));
+  } else if constexpr (B == 3) {
+    if (i < 3) return dense_int_bf16_at<3, 0>(field_pair<3>(w, P, kMagicBf));
+    if (i < 6) return dense_int_bf16_at<3, 3>(field_pair<3>(w, P, kMagicBf));
+    return dense_int_bf16_at<3, 0>((field_pair<3>(w, P, 0u) >> 6) | kMagicBf);
+  } else if constexpr (B == 2) {
+    const uint32_t x = field_pair<2>(w, P, kMagicBf);
+    switch (kstep_offset<2>(i)) {
+      case 0: return dense_int_bf16_at<2, 0>(x);
+      case 2: return dense_int_bf16_at<2, 2>(x);
+      default: return dense_int_bf16_at<2, 4>(x);
+    }
+  } else {
+    return dense_int_bf16_at<6, 0>(field_pair<6>(w, P, kMagicBf));
+  }
+}
+
 // scale2: dense_scale() of the row's scale
 template <int B, bool BF16>
 __device__ __forceinline__ uint32_t dense_pair(const uint32_t (&w)[2 * B], int P, uint32_t scale2) {
+  if constexpr (BF16 && B != 8) {
+    const uint32_t vb = dense_int_bf16<B>(w, P);
+    const __nv_bfloat162 r = __hmul2(*reinterpret_cast<const __nv_bfloat162 *>(&scale2), *reinterpret_cast<const __nv_bfloat162 *>(&vb));
+    return *reinterpret_cast<const uint32_t *>(&r);
+  }
   const uint32_t x = field_pair<B>(w, P, kMagic);
   uint32_t v;
   switch (kstep_offset<B>(P >> 2)) {  // a compile-time constant once the caller's loops are unrolled

@@ -10,15 +10,15 @@
 //     (round(scale * (code*2^(8-b) - 128)), fp16 or bf16) and store them K-major into a
 //     shared-memory stage in the canonical no-swizzle UMMA layout (8 x 16-byte core
 //     matrices), with the packed words of the next two or three blocks already in flight;
-//   * one thread of a ninth warp fetches the activation tiles (batch rows x 64 in-features) with TMA
+//   * one thread of the last warp fetches the activation tiles (batch rows x 64 in-features) with TMA
 //     (cp.async.bulk.tensor.2d, 128-byte swizzle, rows past the batch filled with zeros), as far ahead as
-//     the pipeline has stages, and issues tcgen05.mma (M = 128 weight rows, N = batch rows, K = 16)
+//     the pipeline has stages; an elected lane of the warp before it issues tcgen05.mma (M = 128 weight rows, N = batch rows, K = 16)
 //     from shared-memory descriptors; D[128, N] lives in tensor memory; completion of a stage's MMAs
 //     releases the stage through tcgen05.commit -> mbarrier;
 //   * the epilogue reads D with tcgen05.ld (each warp its own 32 TMEM lanes), converts
-//     and stores y[m, n] (the transpose of D), or, when K is split over several CTAs,
-//     stores fp32 partial sums into caller-provided scratch memory that a second small
-//     kernel adds up in a fixed order.
+//     and stores y[m, n] (the transpose of D); when K is split, the CTAs that share a tile form a
+//     thread-block cluster, leave their fp32 sums in shared memory, and each adds and stores a share
+//     of the batch rows through distributed shared memory, in the order of the K ranges.
 //
 // Every mbarrier wait is bounded (async.cuh); tensor memory is freed on every path.
 #include <cuda.h>  // CUtensorMap and its enums; cuTensorMapEncodeTiled is resolved at run time
@@ -37,17 +37,16 @@ namespace mg {
 constexpr int kTcChunkStride = 2080;   // bytes between 16-byte K chunks of the A stage: 128 rows * 16 B + 32 B
                                        // (the 32 bytes spread the four k-chunks a warp stores at once over all banks)
 constexpr int kTcAStageBytes = 8 * kTcChunkStride;  // 8 chunks of 8 in-features
-constexpr int kTcThreads = 9 * 32;  // 8 producer warps and the MMA issuer
 
 struct GemmParams {
   const uint32_t *w;
   const uint16_t *s;
   const uint16_t *x;
   uint16_t *y;
-  float *partial;  // [split][M][N] fp32 when split > 1
   int N, K, M;
   int ldy;      // elements between two rows of y (N unless the call writes a column block of a wider output)
   int kblocks;  // K / 128
+  float *partial;  // null: the CTAs along K add their sums inside a cluster; else [split][M][N] fp32 scratch for them
   int split;    // CTAs along K
   int ncols;    // UMMA N: batch rows per pass rounded up to 16
   int stages;
@@ -89,6 +88,19 @@ __device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t desc_a, uint6
       : "memory");
 }
 
+// true in exactly one lane of a converged warp
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred;
+  asm volatile(
+      "{\n"
+      "  .reg .pred p;\n"
+      "  elect.sync _|p, 0xffffffff;\n"
+      "  selp.u32 %0, 1, 0, p;\n"
+      "}\n"
+      : "=r"(pred));
+  return pred != 0;
+}
+
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
@@ -103,6 +115,29 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
         "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
       : "r"(taddr));
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+template <bool BF16> __device__ __forceinline__ uint16_t to_out16(float f) {
+  return BF16 ? __bfloat16_as_ushort(__float2bfloat16_rn(f)) : __half_as_ushort(__float2half_rn(f));
+}
+
+// every thread of every CTA of the cluster; orders shared-memory writes before the other CTAs' reads
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
+// address of this CTA's shared-memory location `addr` in the CTA of rank `cta` of the cluster
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t addr, int cta) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(cta));
+  return r;
+}
+
+__device__ __forceinline__ float ld_cluster_f32(uint32_t addr) {
+  float v;
+  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(addr) : "memory");
+  return v;
 }
 
 // shared-memory plan (host and device)
@@ -127,13 +162,22 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&v)[16]) {
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
+__device__ __forceinline__ uint16_t ldg_u16_tc(const uint16_t *p) {
+  uint16_t r;
+  asm volatile("ld.global.nc.u16 %0, [%1];" : "=h"(r) : "l"(p));
+  return r;
+}
+
 // scale groups per 128-wide block
 template <int GS> struct TcScales {
   static constexpr int NG = (GS == 32) ? 4 : 1;
 };
 
-template <int B, int GS, bool BF16>
-__global__ void __launch_bounds__(kTcThreads, 2) gemm_tc_kernel(const GemmParams p, const __grid_constant__ CUtensorMap xmap) {
+// PW producer warps: 8 (each decodes both 64-wide halves of its blocks; two CTAs share an SM) or 16 (warps w and
+// w + 8 share a row tile and take one half each, so that a CTA that has the SM to itself overlaps the latency of
+// one stage with the work of the next).
+template <int B, int GS, bool BF16, int PW>
+__global__ void __launch_bounds__((PW + 2) * 32, PW == 8 ? 2 : 1) gemm_tc_kernel(const GemmParams p, const __grid_constant__ CUtensorMap xmap) {
   extern __shared__ unsigned char tc_smem_raw[];
   const uint32_t raw_u32 = smem_u32(tc_smem_raw);
   const uint32_t base_u32 = (raw_u32 + 1023u) & ~1023u;
@@ -159,7 +203,7 @@ __global__ void __launch_bounds__(kTcThreads, 2) gemm_tc_kernel(const GemmParams
   int tmem_cols = 32;
   while (tmem_cols < p.ncols) tmem_cols <<= 1;
 
-  if (warp == 8) {
+  if (warp == PW) {
     if (lane == 0) {
       for (int i = 0; i < stages; ++i) {
         mbar_init(bar_full + i * 8, 9);  // the eight producer warps and the thread that requests the activations
@@ -177,14 +221,16 @@ __global__ void __launch_bounds__(kTcThreads, 2) gemm_tc_kernel(const GemmParams
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem_base = *tmem_slot;
 
-  // The activations may come from the kernel launched just before this one.
+  // Programmatic dependent launch: the producers only read weights and scales, which no kernel writes, so they
+  // start at once; the thread that fetches the activations waits for the previous kernel before its first
+  // request, and the producers wait before the epilogue writes anything.
   asm volatile("griddepcontrol.launch_dependents;");
-  asm volatile("griddepcontrol.wait;" ::: "memory");
 
   bool failed = false;
-  if (warp < 8) {
+  if (warp < PW) {
     // ------------------------------------------------------------------ producers
-    const int tile16 = tile128 * 8 + warp;
+    const int ptile = warp & 7, my_half = warp >> 3;
+    const int tile16 = tile128 * 8 + ptile;
     const bool valid = tile16 < p.N / 16;
     constexpr int BW = BlockTraits<B>::WORDS;
     constexpr int NG = TcScales<GS>::NG;
@@ -192,17 +238,19 @@ __global__ void __launch_bounds__(kTcThreads, 2) gemm_tc_kernel(const GemmParams
     // loop is unrolled so that no register is copied while its load is still outstanding.  Everything
     // inside the loop is a per-lane base plus a running offset: no multiplications, divisions or
     // modulo by the (runtime) number of stages.
-    constexpr int kAhead = (B >= 6) ? 2 : 3;
+    constexpr int kAhead = (B >= 6) ? 3 : (PW == 16 ? 4 : 6);
     const uint32_t *wnext = p.w + (static_cast<size_t>(valid ? tile16 : 0) * p.kblocks + kb_lo) * BW;  // next block to load
     const uint16_t *snext = p.s + (static_cast<size_t>(valid ? tile16 : 0) * groups + ((GS == -1) ? 0 : kb_lo * NG)) * 16 + g;
     uint32_t wq[kAhead][2 * B];
-    uint32_t sq_lo[kAhead][NG], sq_hi[kAhead][NG];  // dense_scale() of the scales of rows g and g+8
-    auto load_next = [&](uint32_t (&wdst)[2 * B], uint32_t (&lo)[NG], uint32_t (&hi)[NG]) {
+    // raw scales of rows g and g+8, loaded with the block's words and only touched when the block is decoded
+    // (dense_scale() applied on arrival would stall the warp on the load it has just issued)
+    uint16_t sq_lo[kAhead][NG], sq_hi[kAhead][NG];
+    auto load_next = [&](uint32_t (&wdst)[2 * B], uint16_t (&lo)[NG], uint16_t (&hi)[NG]) {
       load_block<B>(wnext, lane, wdst);
 #pragma unroll
       for (int j = 0; j < NG; ++j) {
-        lo[j] = dense_scale<B, BF16>(__ldg(snext + j * 16));
-        hi[j] = dense_scale<B, BF16>(__ldg(snext + j * 16 + 8));
+        lo[j] = ldg_u16_tc(snext + j * 16);
+        hi[j] = ldg_u16_tc(snext + j * 16 + 8);
       }
       wnext += BW;
       if (GS != -1) snext += NG * 16;
@@ -213,7 +261,7 @@ __global__ void __launch_bounds__(kTcThreads, 2) gemm_tc_kernel(const GemmParams
 
     const uint32_t ring_bytes = static_cast<uint32_t>(stages) * plan.stage_bytes;
     // this lane's 16 bytes of rows g and g+8 in the A tile of stage 0, chunk t
-    unsigned char *a_lane = base + plan.off_stages + plan.b_stage_bytes + t * kTcChunkStride + (2 * warp) * 128 + g * 16;
+    unsigned char *a_lane = base + plan.off_stages + plan.b_stage_bytes + t * kTcChunkStride + (2 * ptile) * 128 + g * 16;
     uint32_t cur_stage_off = 0, cur_bar = bar_full, cur_empty = bar_empty, cur_parity = 1;
     int blocks_left = nblk, loads_left = nblk - kAhead;
     while (blocks_left > 0 && !failed) {
@@ -222,6 +270,7 @@ __global__ void __launch_bounds__(kTcThreads, 2) gemm_tc_kernel(const GemmParams
         if (blocks_left > 0 && !failed) {
 #pragma unroll
           for (int h = 0; h < 2; ++h) {
+            if (PW == 8 || h == my_half) {
             if (!mbar_wait(cur_empty, cur_parity)) {  // the tensor pipe is done with what this stage held
               failed = true;
               break;
@@ -231,15 +280,16 @@ __global__ void __launch_bounds__(kTcThreads, 2) gemm_tc_kernel(const GemmParams
 #pragma unroll
               for (int jj = 2 * h; jj < 2 * h + 2; ++jj) {
                 const int gi = (GS == 32) ? jj : 0;
+                const uint32_t s_lo = dense_scale<B, BF16>(sq_lo[a][gi]), s_hi = dense_scale<B, BF16>(sq_hi[a][gi]);
                 uint4 lo, hi;
-                lo.x = dense_pair<B, BF16>(wq[a], 8 * jj + 0, sq_lo[a][gi]);
-                lo.y = dense_pair<B, BF16>(wq[a], 8 * jj + 2, sq_lo[a][gi]);
-                lo.z = dense_pair<B, BF16>(wq[a], 8 * jj + 4, sq_lo[a][gi]);
-                lo.w = dense_pair<B, BF16>(wq[a], 8 * jj + 6, sq_lo[a][gi]);
-                hi.x = dense_pair<B, BF16>(wq[a], 8 * jj + 1, sq_hi[a][gi]);
-                hi.y = dense_pair<B, BF16>(wq[a], 8 * jj + 3, sq_hi[a][gi]);
-                hi.z = dense_pair<B, BF16>(wq[a], 8 * jj + 5, sq_hi[a][gi]);
-                hi.w = dense_pair<B, BF16>(wq[a], 8 * jj + 7, sq_hi[a][gi]);
+                lo.x = dense_pair<B, BF16>(wq[a], 8 * jj + 0, s_lo);
+                lo.y = dense_pair<B, BF16>(wq[a], 8 * jj + 2, s_lo);
+                lo.z = dense_pair<B, BF16>(wq[a], 8 * jj + 4, s_lo);
+                lo.w = dense_pair<B, BF16>(wq[a], 8 * jj + 6, s_lo);
+                hi.x = dense_pair<B, BF16>(wq[a], 8 * jj + 1, s_hi);
+                hi.y = dense_pair<B, BF16>(wq[a], 8 * jj + 3, s_hi);
+                hi.z = dense_pair<B, BF16>(wq[a], 8 * jj + 5, s_hi);
+                hi.w = dense_pair<B, BF16>(wq[a], 8 * jj + 7, s_hi);
                 unsigned char *dst = a_lane + cur_stage_off + (jj & 1) * (4 * kTcChunkStride);
                 *reinterpret_cast<uint4 *>(dst) = lo;
                 *reinterpret_cast<uint4 *>(dst + 128) = hi;
@@ -248,6 +298,7 @@ __global__ void __launch_bounds__(kTcThreads, 2) gemm_tc_kernel(const GemmParams
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy stores -> tensor pipe reads
             __syncwarp();
             if (lane == 0) mbar_arrive(cur_bar);
+            }
             cur_stage_off += plan.stage_bytes;
             cur_bar += 8;
             cur_empty += 8;
@@ -266,22 +317,23 @@ __global__ void __launch_bounds__(kTcThreads, 2) gemm_tc_kernel(const GemmParams
       }
     }
     if (failed) report_status(kStatusMmaTimeout);
-  } else if (warp == 8 && lane == 0) {
-    // ------------------------------------------------------------------ MMA issuer
-    const uint32_t idesc = umma_instr_desc(BF16 ? 1 : 0, p.ncols);
-    uint32_t st_off = 0, st_idx8 = 0, parity = 0;
+  } else if (warp == PW + 1 && lane == 0) {
+    // ------------------------------------------------------------------ activation tiles
+    // Iteration j needs rows m0.. and in-features (kb_lo*128 + 64 j ..+64) in the B part of its stage; each tile is
+    // requested as soon as the tensor pipe has released the stage, so the requests run the whole ring ahead.
+    asm volatile("griddepcontrol.wait;" ::: "memory");  // the activations may come from the kernel launched just before
     const uint32_t ring_bytes = static_cast<uint32_t>(stages) * plan.stage_bytes;
-    // Activation tiles: iteration j needs rows m0.. and in-features (kb_lo*128 + 64 j ..+64) in the B part of its
-    // stage.  They are requested a few iterations ahead, each after the stage has been released.
     uint32_t rq_off = 0, rq_idx8 = 0, rq_parity = 1;
-    int rq_x = kb_lo * 128, rq_left = nit;
-    auto request_x = [&]() -> bool {
-      if (rq_left <= 0) return true;
-      if (!mbar_wait(bar_empty + rq_idx8, rq_parity)) return false;
+    int rq_x = kb_lo * 128;
+    for (int j = 0; j < nit; ++j) {
+      if (!mbar_wait(bar_empty + rq_idx8, rq_parity)) {
+        failed = true;
+        report_status(kStatusMmaTimeout);
+        break;
+      }
       mbar_arrive_expect_tx(bar_full + rq_idx8, plan.b_stage_bytes);
       tma_load_2d(base_u32 + plan.off_stages + rq_off, &xmap, rq_x, m0, bar_full + rq_idx8);
       rq_x += 64;
-      --rq_left;
       rq_off += plan.stage_bytes;
       rq_idx8 += 8;
       if (rq_off == ring_bytes) {
@@ -289,85 +341,117 @@ __global__ void __launch_bounds__(kTcThreads, 2) gemm_tc_kernel(const GemmParams
         rq_idx8 = 0;
         rq_parity ^= 1;
       }
-      return true;
-    };
-    // two stages short of the ring, so that the wait inside request_x() is for MMAs issued two iterations ago
-    const int ahead = stages > 3 ? stages - 2 : 1;
-    for (int j = 0; j < ahead; ++j)
-      if (!request_x()) failed = true;
-    for (int it = 0; it < nit && !failed; ++it) {
-      if (!request_x()) {
-        failed = true;
-        report_status(kStatusMmaTimeout);
-        break;
-      }
+    }
+  } else if (warp == PW) {
+    // ------------------------------------------------------------------ MMA issuer
+    // The whole warp runs the loop, so that addresses and descriptors are warp-uniform values, and one elected
+    // lane issues.  One thread issues every MMA, so this loop is the pipeline's clock: the descriptors of stage 0 are built once
+    // and a stage or a K step only adds to their address field (bits 0..13, in units of 16 bytes).
+    const uint32_t idesc = umma_instr_desc(BF16 ? 1 : 0, p.ncols);
+    const uint32_t ring16 = static_cast<uint32_t>(stages) * plan.stage_bytes >> 4, stage16 = plan.stage_bytes >> 4;
+    const uint32_t stage0_b = base_u32 + plan.off_stages;
+    const uint64_t da0 = umma_smem_desc(stage0_b + plan.b_stage_bytes, kTcChunkStride, 128, 0);
+    const uint64_t db0 = umma_smem_desc(stage0_b, 16, 1024, 2);
+    uint32_t st16 = 0, st_idx8 = 0, parity = 0, accumulate = 0;
+    for (int it = 0; it < nit; ++it) {
       if (!mbar_wait(bar_full + st_idx8, parity)) {
         failed = true;
         report_status(kStatusWeightCopyTimeout);
         break;
       }
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      const uint32_t stage_b = base_u32 + plan.off_stages + st_off;
-      const uint32_t stage_a = stage_b + plan.b_stage_bytes;
+      const uint64_t da = da0 + st16, db = db0 + st16;
+      if (elect_one()) {
 #pragma unroll
-      for (int k = 0; k < 4; ++k) {
-        const uint64_t da = umma_smem_desc(stage_a + 2 * k * kTcChunkStride, kTcChunkStride, 128, 0);
-        const uint64_t db = umma_smem_desc(stage_b + k * 32, 16, 1024, 2);
-        umma_f16(tmem_base, da, db, idesc, (it > 0 || k > 0) ? 1u : 0u);
+        for (int k = 0; k < 4; ++k)
+          umma_f16(tmem_base, da + static_cast<uint64_t>(k * (2 * kTcChunkStride / 16)), db + static_cast<uint64_t>(k * 2), idesc,
+                   (k > 0) ? 1u : accumulate);
+        umma_commit(bar_empty + st_idx8);
       }
-      umma_commit(bar_empty + st_idx8);
-      st_off += plan.stage_bytes;
+      accumulate = 1;
+      __syncwarp();
+      st16 += stage16;
       st_idx8 += 8;
-      if (st_off == ring_bytes) {
-        st_off = 0;
+      if (st16 == ring16) {
+        st16 = 0;
         st_idx8 = 0;
         parity ^= 1;
       }
     }
-    if (!failed) umma_commit(bar_done);
+    if (!failed && elect_one()) umma_commit(bar_done);
+    __syncwarp();
   }
 
   // ---------------------------------------------------------------------- epilogue
-  if (warp < 8 && !failed) {
+  if (warp < PW) asm volatile("griddepcontrol.wait;" ::: "memory");  // nothing is written before the previous kernel is done
+  if (warp < PW && !failed) {
     if (!mbar_wait(bar_done, 0)) {
       failed = true;
       report_status(kStatusMmaTimeout);
     }
   }
-  if (warp < 8 && !failed) {
+  // the pipeline's stages are free once every MMA is done; with K split they hold this CTA's fp32 partial sums
+  float *staging = reinterpret_cast<float *>(base + plan.off_stages);
+  if (warp < PW && !failed) {
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const int q = warp & 3;
     const int n = tile128 * 128 + q * 32 + lane;
     const int nchunks = p.ncols / 16;
-    for (int ci = (warp >> 2); ci < nchunks; ci += 2) {
+    for (int ci = (warp >> 2); ci < nchunks; ci += PW / 4) {
       uint32_t v[16];
       tmem_ld16(tmem_base + (static_cast<uint32_t>(q * 32) << 16) + ci * 16, v);
-      if (n < p.N) {
+      if (p.split > 1 && p.partial == nullptr) {
+        // this CTA's share of the sum over K: staging[batch row][out-feature of the tile], fp32
+#pragma unroll
+        for (int j = 0; j < 16; ++j) staging[(ci * 16 + j) * 128 + q * 32 + lane] = __uint_as_float(v[j]);
+      } else if (p.split > 1) {
+        if (n < p.N) {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const int m = m0 + ci * 16 + j;
+            if (m < m0 + mrows) p.partial[(static_cast<size_t>(sk) * p.M + m) * p.N + n] = __uint_as_float(v[j]);
+          }
+        }
+      } else if (n < p.N) {
 #pragma unroll
         for (int j = 0; j < 16; ++j) {
           const int m = m0 + ci * 16 + j;
-          if (m < m0 + mrows) {
-            const float f = __uint_as_float(v[j]);
-            if (p.split > 1) {
-              p.partial[(static_cast<size_t>(sk) * p.M + m) * p.N + n] = f;
-            } else if (BF16) {
-              p.y[static_cast<size_t>(m) * p.ldy + n] = __bfloat16_as_ushort(__float2bfloat16_rn(f));
-            } else {
-              p.y[static_cast<size_t>(m) * p.ldy + n] = __half_as_ushort(__float2half_rn(f));
-            }
-          }
+          if (m < m0 + mrows) p.y[static_cast<size_t>(m) * p.ldy + n] = to_out16<BF16>(__uint_as_float(v[j]));
         }
       }
     }
   }
+  if (p.split > 1 && p.partial == nullptr) {
+    // The CTAs that share a tile form one cluster along K.  Each adds, in the order of the K ranges, the batch
+    // rows it owns from every CTA's staging area through distributed shared memory, and stores them.
+    __syncwarp();
+    cluster_sync_all();
+    if (warp < PW) {
+      const int per = (p.ncols + p.split - 1) / p.split;
+      const int c_lo = sk * per, c_hi = min(c_lo + per, p.ncols);
+      for (int idx = tid; idx < (c_hi - c_lo) * 128; idx += PW * 32) {
+        const int c = c_lo + (idx >> 7), nn = idx & 127;
+        const int m = m0 + c, n = tile128 * 128 + nn;
+        if (m < m0 + mrows && n < p.N) {
+          const uint32_t local = smem_u32(staging + c * 128 + nn);
+          float sum = 0.f;
+          for (int s = 0; s < p.split; ++s) sum += ld_cluster_f32(map_to_cta(local, s));
+          p.y[static_cast<size_t>(m) * p.ldy + n] = to_out16<BF16>(sum);
+        }
+      }
+    }
+    __syncwarp();
+    cluster_sync_all();  // nobody leaves while its staging area is still being read
+  }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
-  if (warp == 8) {
+  if (warp == PW) {
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(tmem_cols) : "memory");
   }
 }
 
-// partial[split][M][N] fp32 -> y[M][N] (rows ldy elements apart), added in a fixed order
+// partial[split][M][N] fp32 -> y[M][N] (rows ldy elements apart), added in the order of the K ranges: the second
+// kernel of a K split that goes through scratch memory
 template <bool BF16>
 __global__ void splitk_reduce_kernel(const float *__restrict__ partial, uint16_t *__restrict__ y, long long mn, int split,
                                      int n_cols, int ldy) {
@@ -379,7 +463,7 @@ __global__ void splitk_reduce_kernel(const float *__restrict__ partial, uint16_t
     float sum = 0.f;
     for (int s = 0; s < split; ++s) sum += partial[static_cast<long long>(s) * mn + i];
     const long long m = i / n_cols;
-    y[m * ldy + (i - m * n_cols)] = BF16 ? __bfloat16_as_ushort(__float2bfloat16_rn(sum)) : __half_as_ushort(__float2half_rn(sum));
+    y[m * ldy + (i - m * n_cols)] = to_out16<BF16>(sum);
   }
 }
 
@@ -406,6 +490,7 @@ int gemm_tc_pick_split(int N, int K, int M, int sm_count) {
   return split;
 }
 
+// Scratch for a K split that goes through global memory (scratch_reduce, or a device that cannot place the cluster).
 long long gemm_tc_workspace_bytes(int N, int K, int M, int sm_count) {
   const int split = gemm_tc_pick_split(N, K, M, sm_count);
   return split > 1 ? static_cast<long long>(split) * M * N * 4 : 0;
@@ -435,14 +520,13 @@ static int make_x_tensor_map(CUtensorMap *map, const void *x, int M, int K, int 
   return r == CUDA_SUCCESS ? MG_OK : MG_ERR_CUDA;
 }
 
-template <int B, int GS, bool BF16>
-static int launch_gemm_tc(GemmParams p, cudaStream_t stream, bool pdl) {
-  auto kernel = gemm_tc_kernel<B, GS, BF16>;
-  p.ncols = round_up16(p.M < 256 ? p.M : 256);
+template <int B, int GS, bool BF16, int PW>
+static int launch_gemm_tc_warps(GemmParams p, cudaStream_t stream, bool pdl, float *fallback_partial) {
+  auto kernel = gemm_tc_kernel<B, GS, BF16, PW>;
   CUtensorMap xmap;
   if (make_x_tensor_map(&xmap, p.x, p.M, p.K, p.ncols) != MG_OK) return MG_ERR_CUDA;
   int stages = 8;
-  if (tc_two_ctas_per_sm(p.ncols)) {
+  if (PW == 8) {
     while (stages > 3 && tc_plan(p.ncols, stages).total > kTcHalfSmBytes) --stages;
   } else {
     while (stages > 2 && tc_plan(p.ncols, stages).total > 2 * kTcHalfSmBytes) --stages;
@@ -456,20 +540,37 @@ static int launch_gemm_tc(GemmParams p, cudaStream_t stream, bool pdl) {
   }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((p.N + 127) / 128, p.split, (p.M + 255) / 256);
-  cfg.blockDim = dim3(kTcThreads, 1, 1);
+  cfg.blockDim = dim3((PW + 2) * 32, 1, 1);
   cfg.dynamicSmemBytes = plan.total;
   cfg.stream = stream;
-  cudaLaunchAttribute attrs[1];
+  cudaLaunchAttribute attrs[2];
   int na = 0;
   if (pdl) {
     attrs[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attrs[na].val.programmaticStreamSerializationAllowed = 1;
     ++na;
   }
+  if (p.split > 1 && p.partial == nullptr) {  // the CTAs along K form a cluster and add their sums through distributed shared memory
+    attrs[na].id = cudaLaunchAttributeClusterDimension;
+    attrs[na].val.clusterDim.x = 1;
+    attrs[na].val.clusterDim.y = static_cast<unsigned>(p.split);
+    attrs[na].val.clusterDim.z = 1;
+    ++na;
+  }
   cfg.attrs = attrs;
   cfg.numAttrs = na;
-  if (cudaLaunchKernelEx(&cfg, kernel, p, xmap) != cudaSuccess) return MG_ERR_CUDA;
-  if (p.split > 1) {
+  if (cudaLaunchKernelEx(&cfg, kernel, p, xmap) != cudaSuccess) {
+    if (p.split > 1 && p.partial == nullptr && fallback_partial != nullptr) {
+      // the device could not place the cluster (a partitioned GPU, say): go through the caller's scratch instead
+      (void)cudaGetLastError();
+      p.partial = fallback_partial;
+      cfg.numAttrs = pdl ? 1 : 0;
+      if (cudaLaunchKernelEx(&cfg, kernel, p, xmap) != cudaSuccess) return MG_ERR_CUDA;
+    } else {
+      return MG_ERR_CUDA;
+    }
+  }
+  if (p.split > 1 && p.partial != nullptr) {
     const long long mn = static_cast<long long>(p.M) * p.N;
     long long blocks = (mn + 255) / 256;
     if (blocks > 148 * 8) blocks = 148 * 8;
@@ -488,27 +589,43 @@ static int launch_gemm_tc(GemmParams p, cudaStream_t stream, bool pdl) {
   return MG_OK;
 }
 
+// Sixteen producer warps when the CTA has its SM to itself: the stages are too large for two CTAs per SM, or there
+// are no more CTAs than SMs.
+template <int B, int GS, bool BF16>
+static int launch_gemm_tc(GemmParams p, cudaStream_t stream, bool pdl, float *fallback_partial) {
+  p.ncols = round_up16(p.M < 256 ? p.M : 256);
+  int sm_count = 0;
+  {
+    const int st = current_device_sm_count(&sm_count);
+    if (st != MG_OK) return st;
+  }
+  const long long ctas = static_cast<long long>((p.N + 127) / 128) * p.split * ((p.M + 255) / 256);
+  if (!tc_two_ctas_per_sm(p.ncols) || ctas <= sm_count) return launch_gemm_tc_warps<B, GS, BF16, 16>(p, stream, pdl, fallback_partial);
+  return launch_gemm_tc_warps<B, GS, BF16, 8>(p, stream, pdl, fallback_partial);
+}
+
 template <int B, int GS>
-static int launch_gemm_tc_type(const GemmParams &p, bool bf16, cudaStream_t stream, bool pdl) {
-  if (bf16) return launch_gemm_tc<B, GS, true>(p, stream, pdl);
-  return launch_gemm_tc<B, GS, false>(p, stream, pdl);
+static int launch_gemm_tc_type(const GemmParams &p, bool bf16, cudaStream_t stream, bool pdl, float *fb) {
+  if (bf16) return launch_gemm_tc<B, GS, true>(p, stream, pdl, fb);
+  return launch_gemm_tc<B, GS, false>(p, stream, pdl, fb);
 }
 
 template <int B>
-static int launch_gemm_tc_group(const GemmParams &p, int group_size, bool bf16, cudaStream_t stream, bool pdl) {
+static int launch_gemm_tc_group(const GemmParams &p, int group_size, bool bf16, cudaStream_t stream, bool pdl, float *fb) {
   switch (group_size) {
-    case -1: return launch_gemm_tc_type<B, -1>(p, bf16, stream, pdl);
-    case 32: return launch_gemm_tc_type<B, 32>(p, bf16, stream, pdl);
-    case 128: return launch_gemm_tc_type<B, 128>(p, bf16, stream, pdl);
+    case -1: return launch_gemm_tc_type<B, -1>(p, bf16, stream, pdl, fb);
+    case 32: return launch_gemm_tc_type<B, 32>(p, bf16, stream, pdl, fb);
+    case 128: return launch_gemm_tc_type<B, 128>(p, bf16, stream, pdl, fb);
     default: return MG_ERR_BAD_ARG;
   }
 }
 
-// workspace: fp32 scratch of at least gemm_tc_workspace_bytes(), or null to run without a K split
+// workspace: fp32 scratch of at least gemm_tc_workspace_bytes() or null.  The sums of a split K meet inside a
+// thread-block cluster; the scratch is used when scratch_reduce asks for it, or when the cluster cannot be launched.
 int gemm_tc_launch(int bitwidth, int group_size, int N, int K, int M, const void *w, const void *s, const void *x,
                    void *y, void *workspace, long long workspace_bytes, bool bf16, bool pdl, int split_override,
-                   cudaStream_t stream, int ldy) {
-  int sm_count = 0;  // of the current device: the same value matgptq_b200_matmul_workspace_bytes sized the scratch with
+                   cudaStream_t stream, int ldy, bool scratch_reduce) {
+  int sm_count = 0;  // of the current device
   {
     const int st = current_device_sm_count(&sm_count);
     if (st != MG_OK) return st;
@@ -518,7 +635,6 @@ int gemm_tc_launch(int bitwidth, int group_size, int N, int K, int M, const void
   p.s = static_cast<const uint16_t *>(s);
   p.x = static_cast<const uint16_t *>(x);
   p.y = static_cast<uint16_t *>(y);
-  p.partial = static_cast<float *>(workspace);
   p.N = N;
   p.K = K;
   p.M = M;
@@ -526,19 +642,20 @@ int gemm_tc_launch(int bitwidth, int group_size, int N, int K, int M, const void
   p.kblocks = K / 128;
   int split = split_override > 0 ? split_override : gemm_tc_pick_split(N, K, M, sm_count);
   if (split > p.kblocks) split = p.kblocks;
-  if (split > 1 && (workspace == nullptr || workspace_bytes < static_cast<long long>(split) * M * N * 4)) {
-    if (split_override > 0) return MG_ERR_BAD_ARG;
-    split = 1;  // no scratch given: every CTA runs the whole K range
-  }
+  if (split > 8) return MG_ERR_BAD_ARG;  // the CTAs along K form one cluster
+  const bool have_scratch = workspace != nullptr && workspace_bytes >= static_cast<long long>(split) * M * N * 4;
+  if (scratch_reduce && split > 1 && !have_scratch) return MG_ERR_BAD_ARG;
+  p.partial = (scratch_reduce && split > 1) ? static_cast<float *>(workspace) : nullptr;
+  float *fb = (split > 1 && have_scratch) ? static_cast<float *>(workspace) : nullptr;
   p.split = split;
   p.ncols = 0;
   p.stages = 0;
   switch (bitwidth) {
-    case 2: return launch_gemm_tc_group<2>(p, group_size, bf16, stream, pdl);
-    case 3: return launch_gemm_tc_group<3>(p, group_size, bf16, stream, pdl);
-    case 4: return launch_gemm_tc_group<4>(p, group_size, bf16, stream, pdl);
-    case 6: return launch_gemm_tc_group<6>(p, group_size, bf16, stream, pdl);
-    case 8: return launch_gemm_tc_group<8>(p, group_size, bf16, stream, pdl);
+    case 2: return launch_gemm_tc_group<2>(p, group_size, bf16, stream, pdl, fb);
+    case 3: return launch_gemm_tc_group<3>(p, group_size, bf16, stream, pdl, fb);
+    case 4: return launch_gemm_tc_group<4>(p, group_size, bf16, stream, pdl, fb);
+    case 6: return launch_gemm_tc_group<6>(p, group_size, bf16, stream, pdl, fb);
+    case 8: return launch_gemm_tc_group<8>(p, group_size, bf16, stream, pdl, fb);
     default: return MG_ERR_BAD_ARG;
   }
 }

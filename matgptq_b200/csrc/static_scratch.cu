@@ -1,17 +1,18 @@
 // Packed matmul for callers that must not allocate device memory.
 //
-// The tensor-core path splits K over several CTAs for shapes with few 128-row tiles and
-// then needs fp32 scratch for the partial sums (gemm_tc.cu).  matgptq_b200_matmul_ws takes
-// that scratch from the caller.  Some callers have none to give and cannot get any: a
-// serving process whose memory pool was sized up front and already owns the whole device, a
-// plugin called from inside such a host without access to its allocator, or a latency-critical
-// loop in which cudaMalloc (which synchronises the device) is forbidden.  For them the scratch
-// lives in the library image itself: a fixed array in device global memory.  The CUDA runtime
-// loads device code lazily and this file has no kernel of its own, so the array comes into a
-// GPU's memory when its address is first asked for on that GPU (the first call below that needs
-// scratch there), and stays until the process exits.  That first call is the only one that can
-// change the amount of free device memory; it has to come before the host hands the rest of
-// the device to its pool.
+// The tensor-core path splits K over several CTAs for shapes with few 128-row tiles (gemm_tc.cu).
+// Their fp32 sums normally meet inside a thread-block cluster; they go through scratch memory and a
+// second kernel when the caller asks for that form (MATGPTQ_B200_FLAG_SCRATCH_REDUCE) or when the
+// device cannot place the cluster.  matgptq_b200_matmul_ws takes that scratch from the caller.  Some
+// callers have none to give and cannot get any: a serving process whose memory pool was sized up
+// front and already owns the whole device, a plugin called from inside such a host without access
+// to its allocator, or a latency-critical loop in which cudaMalloc (which synchronises the device)
+// is forbidden.  For them the scratch lives in the library image itself: a fixed array in device
+// global memory.  The CUDA runtime loads device code lazily and this file has no kernel of its
+// own, so the array comes into a GPU's memory when its address is first asked for on that GPU (the
+// first call below for a shape that splits K), and stays until the process exits.  That first call
+// is the only one that can change the amount of free device memory; it has to come before the
+// host hands the rest of the device to its pool.
 #include <cuda_runtime.h>
 
 #include <mutex>
@@ -56,8 +57,12 @@ int static_scratch_address(void **out) {
 extern "C" int matgptq_b200_matmul_static_scratch(int64_t bitwidth, int64_t group_size, int64_t n_out, int64_t n_in,
                                                    int64_t batch, const void *w, const void *s, const void *x, void *y,
                                                    void *stream, uint32_t flags) {
-  const int64_t need = matgptq_b200_matmul_workspace_bytes(n_out, n_in, batch);
-  if (need > kStaticScratchBytes) return MATGPTQ_B200_ERR_SCRATCH_TOO_SMALL;
+  int64_t need = matgptq_b200_matmul_workspace_bytes(n_out, n_in, batch);
+  if (need > kStaticScratchBytes) {
+    // the sums cannot go through the array; without the flag they do not have to (they meet inside the cluster)
+    if (flags & MATGPTQ_B200_FLAG_SCRATCH_REDUCE) return MATGPTQ_B200_ERR_SCRATCH_TOO_SMALL;
+    need = 0;
+  }
   void *scratch = nullptr;
   if (need > 0) {
     const int st = static_scratch_address(&scratch);

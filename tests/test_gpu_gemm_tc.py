@@ -86,7 +86,9 @@ def test_split_k_and_small_batches_agree_with_gemv(cuda, split, m):
 
 
 def test_workspace_contract(lib, cuda):
-    from matgptq_b200 import ops
+    """The sums of a split K meet inside a thread-block cluster; with FLAG_SCRATCH_REDUCE they go through scratch
+    and a second kernel.  Both add in the order of the K ranges: identical bits."""
+    from matgptq_b200 import _native
     assert lib.matgptq_b200_matmul_workspace_bytes(4096, 4096, 16) == 0      # GEMV family: no scratch
     need = lib.matgptq_b200_matmul_workspace_bytes(1024, 4096, 64)           # 8 tiles only: K is split
     assert need > 0 and need % (64 * 1024 * 4) == 0
@@ -94,22 +96,34 @@ def test_workspace_contract(lib, cuda):
     layer = synth.make_layer(n_out, n_in, 128, seed=1, sym=True, dtype=torch.bfloat16, device=cuda)
     packed, scales_r, flag = _pack(layer, n_out, n_in, 128, b, torch.bfloat16)
     x = synth.make_activations(m, n_in, seed=1, dtype=torch.bfloat16, device=cuda)
-    y_split = torch.ops.matgptq_cuda.matmul_matgptq(x, packed, scales_r, n_out, n_in, b, 128, flag)
-    # no scratch: the plain entry point runs without a K split and must agree
-    y_plain = torch.empty_like(y_split)
+    y_op = torch.ops.matgptq_cuda.matmul_matgptq(x, packed, scales_r, n_out, n_in, b, 128, flag)
+    stream = torch.cuda.current_stream().cuda_stream
+    # no scratch: the plain entry point splits K in the same way
+    y_plain = torch.empty_like(y_op)
     st = lib.matgptq_b200_matmul(b, 128, n_out, n_in, m, packed.data_ptr(), scales_r.data_ptr(), x.data_ptr(),
-                                 y_plain.data_ptr(), torch.cuda.current_stream().cuda_stream, flag)
+                                 y_plain.data_ptr(), stream, flag)
+    assert st == 0
+    # through scratch
+    ws = torch.empty(need, dtype=torch.uint8, device=cuda)
+    y_scratch = torch.empty_like(y_op)
+    st = lib.matgptq_b200_matmul_ws(b, 128, n_out, n_in, m, packed.data_ptr(), scales_r.data_ptr(), x.data_ptr(),
+                                    y_scratch.data_ptr(), stream, flag | _native.FLAG_SCRATCH_REDUCE, ws.data_ptr(), need, 2, 0)
     assert st == 0
     torch.cuda.synchronize()
     w_ref = oracle.dequantize_weight(layer.qweight.cpu(), layer.scales.cpu(), layer.zeros.cpu(), 8, b)
     y_ref = oracle.linear_fp32_accumulate(x.cpu(), w_ref)
-    assert oracle.rel_err(y_split.cpu(), y_ref) <= TOL and oracle.rel_err(y_plain.cpu(), y_ref) <= TOL
-    # a forced split without enough scratch is an argument error, not a silent fallback
+    assert oracle.rel_err(y_op.cpu(), y_ref) <= TOL
+    assert torch.equal(y_op, y_plain) and torch.equal(y_op, y_scratch)
+    # the scratch form without enough scratch, and more CTAs along K than a cluster holds, are argument
+    # errors, not silent fallbacks
     small = torch.empty(16, dtype=torch.uint8, device=cuda)
     st = lib.matgptq_b200_matmul_ws(b, 128, n_out, n_in, m, packed.data_ptr(), scales_r.data_ptr(), x.data_ptr(),
-                                    y_plain.data_ptr(), torch.cuda.current_stream().cuda_stream, flag,
-                                    small.data_ptr(), 16, 2, 4)
+                                    y_plain.data_ptr(), stream, flag | _native.FLAG_SCRATCH_REDUCE, small.data_ptr(), 16, 2, 4)
     assert st == 1
+    st = lib.matgptq_b200_matmul_ws(b, 128, n_out, n_in, m, packed.data_ptr(), scales_r.data_ptr(), x.data_ptr(),
+                                    y_plain.data_ptr(), stream, flag, None, 0, 2, 9)
+    assert st == 1
+    assert _status_ok()
 
 
 _LLAMA = {"q_o": (4096, 4096), "k_v": (4096, 1024), "gate_up": (4096, 14336), "down": (14336, 4096)}

@@ -26,6 +26,9 @@ def _layer(n_out, n_in, b, dtype, seed, cuda):
     return packed, scales_r, flag
 
 
+SCRATCH_REDUCE = 8  # MATGPTQ_B200_FLAG_SCRATCH_REDUCE: the sums of a split K go through the scratch
+
+
 def _both(lib, packed, scales_r, flag, x, n_out, n_in, b):
     m = x.shape[0]
     stream = torch.cuda.current_stream().cuda_stream
@@ -52,18 +55,21 @@ def test_static_scratch_matches_caller_scratch_twice_in_a_row(lib, cuda):
     x_a = synth.make_activations(64, n_in, seed=1, dtype=torch.float16, device=cuda)
     x_b = synth.make_activations(48, n_in, seed=2, dtype=torch.bfloat16, device=cuda)
 
-    y_ws, y_static, need = _both(lib, packed_a, scales_a, flag_a, x_a, n_out, n_in, 4)
+    y_ws, y_static, need = _both(lib, packed_a, scales_a, flag_a | SCRATCH_REDUCE, x_a, n_out, n_in, 4)
     assert need > 0, "this shape is meant to exercise the scratch"
     assert torch.isfinite(y_static.float()).all()
     assert torch.equal(y_static, y_ws)
 
     # second call, other weights, dtype and batch: the array still holds the first call's sums
-    y_ws2, y_static2, need2 = _both(lib, packed_b, scales_b, flag_b, x_b, n_out, n_in, 3)
+    y_ws2, y_static2, need2 = _both(lib, packed_b, scales_b, flag_b | SCRATCH_REDUCE, x_b, n_out, n_in, 3)
     assert need2 > 0
     assert torch.equal(y_static2, y_ws2)
     # and the first problem again gives the first answer again
-    _, y_static3, _ = _both(lib, packed_a, scales_a, flag_a, x_a, n_out, n_in, 4)
+    _, y_static3, _ = _both(lib, packed_a, scales_a, flag_a | SCRATCH_REDUCE, x_a, n_out, n_in, 4)
     assert torch.equal(y_static3, y_ws)
+    # without the flag the sums meet inside the cluster and the array is only a fallback: the same bits
+    y_ws4, y_static4, _ = _both(lib, packed_a, scales_a, flag_a, x_a, n_out, n_in, 4)
+    assert torch.equal(y_static4, y_ws) and torch.equal(y_ws4, y_ws)
     assert _native.device_status() == 0
 
 
@@ -78,17 +84,19 @@ def test_static_scratch_later_calls_leave_free_memory_unchanged(lib, cuda):
     stream = torch.cuda.current_stream().cuda_stream
     assert lib.matgptq_b200_matmul_workspace_bytes(n_out, n_in, m) > 0
 
-    def call():
+    def call(extra=0):
         st = lib.matgptq_b200_matmul_static_scratch(b, 128, n_out, n_in, m, packed.data_ptr(), scales_r.data_ptr(),
-                                                    x.data_ptr(), y.data_ptr(), stream, flag)
+                                                    x.data_ptr(), y.data_ptr(), stream, flag | extra)
         assert st == 0
         torch.cuda.synchronize()
 
     call()  # set-up (if no earlier test did it) happens here
+    call(SCRATCH_REDUCE)  # both forms of the K split have run once: their kernels are loaded
     free_before, _ = torch.cuda.mem_get_info(cuda)
     first = y.clone()
     free_before, _ = torch.cuda.mem_get_info(cuda)  # taken after the clone: nothing below allocates through torch
     call()
+    call(SCRATCH_REDUCE)
     call()
     free_after, _ = torch.cuda.mem_get_info(cuda)
     assert free_after == free_before
@@ -102,15 +110,23 @@ def test_static_scratch_small_batches_and_limit(lib, cuda):
     x = synth.make_activations(8, n_in, seed=3, dtype=torch.float16, device=cuda)
     y_ws, y_static, need = _both(lib, packed, scales_r, flag, x, n_out, n_in, b)
     assert need == 0 and torch.equal(y_static, y_ws)
-    # a shape that wants more than the built-in 8 MiB is refused, and nothing is launched
+    # a shape whose sums want more than the built-in 8 MiB: with the flag it is refused and nothing is launched
     m = 256
     need = lib.matgptq_b200_matmul_workspace_bytes(n_out, n_in, m)
     assert need > 8 * 1024 * 1024
     xb = synth.make_activations(m, n_in, seed=4, dtype=torch.float16, device=cuda)
     y = torch.full((m, n_out), 7.0, dtype=torch.float16, device=cuda)
+    stream = torch.cuda.current_stream().cuda_stream
     st = lib.matgptq_b200_matmul_static_scratch(b, 128, n_out, n_in, m, packed.data_ptr(), scales_r.data_ptr(),
-                                                xb.data_ptr(), y.data_ptr(), torch.cuda.current_stream().cuda_stream, flag)
+                                                xb.data_ptr(), y.data_ptr(), stream, flag | SCRATCH_REDUCE)
     assert st == 5
     assert b"scratch" in lib.matgptq_b200_strerror(st)
     torch.cuda.synchronize()
     assert (y == 7.0).all()
+    # without the flag the sums meet inside the cluster, no scratch is involved, and the call goes through
+    st = lib.matgptq_b200_matmul_static_scratch(b, 128, n_out, n_in, m, packed.data_ptr(), scales_r.data_ptr(),
+                                                xb.data_ptr(), y.data_ptr(), stream, flag)
+    assert st == 0
+    y_ws = torch.ops.matgptq_cuda.matmul_matgptq(xb, packed, scales_r, n_out, n_in, b, 128, flag)
+    torch.cuda.synchronize()
+    assert torch.equal(y, y_ws)
