@@ -600,9 +600,11 @@ def run_decode(world: int, rank: int, dev: torch.device, model_name: str, batch:
 def run_tensor_core_cells(dev: torch.device) -> list:
     """Tensor-core regime: bf16, M in {32,64,128,256}, b in {3,4,8}, next to torch's dense bf16 GEMM on the
     dequantised weights.  Cold L2: launches rotate over copies of the weights."""
-    from matgptq_b200 import ops
+    from matgptq_b200 import _native, ops
     from oracle import matgptq_oracle as oracle
     out = []
+    # launched as the decode harness and the sweep above launch the operator: with programmatic dependent launch
+    tc_flags = _native.FLAG_ASYNC | _native.FLAG_BF16 | _native.FLAG_PDL
     for si, (name, (k, n)) in enumerate(synth.LLAMA3_8B_SHAPES.items()):
         layer = synth.make_layer(n, k, GROUP, seed=300 + si, sym=True, dtype=torch.bfloat16, device=dev)
         rows_dev = torch.linspace(0, n - 1, min(PARITY_SAMPLE_ROWS, n)).long().unique().to(dev)
@@ -621,7 +623,7 @@ def run_tensor_core_cells(dev: torch.device) -> list:
                 ws = torch.empty(max(need, 16), dtype=torch.uint8, device=dev)
 
                 def ours(i):
-                    ops.matmul_matgptq_raw(x, packs[i % copies], scales_r, n, k, b, GROUP, 3, out=y, workspace=ws if need else None)
+                    ops.matmul_matgptq_raw(x, packs[i % copies], scales_r, n, k, b, GROUP, tc_flags, out=y, workspace=ws if need else None)
 
                 def torch_dense(i):
                     torch.matmul(x, denses[i % copies].t(), out=y)

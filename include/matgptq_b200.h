@@ -80,7 +80,7 @@ int matgptq_b200_matmul_tuned(int64_t bitwidth, int64_t group_size, int64_t n_ou
 
 /*
  * The same product with optional scratch memory and a forced path.  Batches of more than 16 rows run
- * on the tensor cores (tcgen05) (from 40 rows for layers with fewer than 2048 out-features, which
+ * on the tensor cores (tcgen05) (from 25 rows for layers with fewer than 2048 out-features, which
  * the GEMV serves faster until then); for shapes with few 128-row tiles that path splits K over
  * up to eight CTAs, which form a thread-block cluster and add their fp32 sums through distributed
  * shared memory, so that no scratch is needed.  Scratch of matgptq_b200_matmul_workspace_bytes(...)

@@ -50,13 +50,14 @@ const char *matgptq_b200_strerror(int status) {
 static const int64_t kTensorCoreMinBatch = 32;
 
 // Automatic choice between the GEMV family and the tensor-core path.  The GEMV handles 16 activation rows per
-// pass, so from 17 rows on it reads the weights twice (from L2) and doubles its tensor work; measured on B200
-// (bf16, group 128, cold L2): q/o 24 rows 14.2 us GEMV against 11.4 us tensor cores, down 32.5 against 24.4,
-// gate/up level; only layers with few row tiles (k/v, N = 1024: 6.6 against 8.3 us at 32 rows, 11.3 against 9.0
-// at 48) are better off on the GEMV up to three passes.
+// pass, so from 17 rows on it reads the weights twice (from L2) and doubles its tensor work, while the time of
+// the tensor-core path hardly depends on the batch; measured on B200 (bf16, 4 bits, group 128, cold L2, GEMV
+// against tensor cores in us): q/o 16 rows 8.0 / 7.8, 24 rows 14.1 / 8.4; gate/up 16 rows 14.7 / 18.1, 24 rows
+// 26.9 / 19.9; down 16 rows 17.7 / 17.0, 24 rows 31.9 / 18.5.  Layers with few row tiles (k/v, N = 1024) are
+// level at 24 rows (5.7 / 5.8) and better off on the tensor cores from 32 (6.5 / 5.9).
 static bool uses_tensor_cores(int64_t n_out, int64_t batch) {
   if (n_out >= 2048) return batch > 16;
-  return batch >= 40;
+  return batch > 24;
 }
 
 static int sm_count_of_current_device(int *out) {

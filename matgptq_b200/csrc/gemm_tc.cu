@@ -173,6 +173,69 @@ template <int GS> struct TcScales {
   static constexpr int NG = (GS == 32) ? 4 : 1;
 };
 
+// 16 bytes to shared memory at addr + OFF (OFF goes into the instruction)
+template <int OFF> __device__ __forceinline__ void sts_v4(uint32_t addr, const uint4 &v) {
+  asm volatile("st.shared.v4.b32 [%0 + %5], {%1, %2, %3, %4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w), "n"(OFF)
+               : "memory");
+}
+
+// Chunk JJ (0..3, 32 in-features) of a block: this lane's dense weights of rows g (lo) and g+8 (hi), eight each, as
+// 16 bytes per row into the A tile whose lane address for chunk 0 is `addr`.
+template <int B, bool BF16, int JJ>
+__device__ __forceinline__ void tc_store_chunk(const uint32_t (&w)[2 * B], uint32_t s_lo, uint32_t s_hi, uint32_t addr) {
+  uint4 lo, hi;
+  lo.x = dense_pair<B, BF16>(w, 8 * JJ + 0, s_lo);
+  lo.y = dense_pair<B, BF16>(w, 8 * JJ + 2, s_lo);
+  lo.z = dense_pair<B, BF16>(w, 8 * JJ + 4, s_lo);
+  lo.w = dense_pair<B, BF16>(w, 8 * JJ + 6, s_lo);
+  hi.x = dense_pair<B, BF16>(w, 8 * JJ + 1, s_hi);
+  hi.y = dense_pair<B, BF16>(w, 8 * JJ + 3, s_hi);
+  hi.z = dense_pair<B, BF16>(w, 8 * JJ + 5, s_hi);
+  hi.w = dense_pair<B, BF16>(w, 8 * JJ + 7, s_hi);
+  sts_v4<(JJ & 1) * 4 * kTcChunkStride>(addr, lo);
+  sts_v4<(JJ & 1) * 4 * kTcChunkStride + 128>(addr, hi);
+}
+
+// Half H (0, 1) of a block = chunks 2H and 2H+1 = one pipeline stage; slo/shi: raw scales of rows g and g+8
+template <int B, int GS, bool BF16, int H>
+__device__ __forceinline__ void tc_store_half(const uint32_t (&w)[2 * B], const uint16_t (&slo)[TcScales<GS>::NG],
+                                              const uint16_t (&shi)[TcScales<GS>::NG], uint32_t addr) {
+  constexpr int g0 = (GS == 32) ? 2 * H : 0, g1 = (GS == 32) ? 2 * H + 1 : 0;
+  const uint32_t lo0 = dense_scale<B, BF16>(slo[g0]), hi0 = dense_scale<B, BF16>(shi[g0]);
+  tc_store_chunk<B, BF16, 2 * H>(w, lo0, hi0, addr);
+  const uint32_t lo1 = (GS == 32) ? dense_scale<B, BF16>(slo[g1]) : lo0, hi1 = (GS == 32) ? dense_scale<B, BF16>(shi[g1]) : hi0;
+  tc_store_chunk<B, BF16, 2 * H + 1>(w, lo1, hi1, addr);
+}
+
+struct TcProducer {
+  uint32_t off, idx8, parity;            // byte offset, barrier offset and empty-barrier parity of the current stage
+  uint32_t stage_bytes, stages8;         // bytes per stage; 8 * number of stages
+  uint32_t bar_full, bar_empty, a_lane;  // shared-memory addresses for stage 0
+};
+
+// One 64-wide half (H = 0, 1) of a block: wait for the stage, decode and store this lane's share, hand the stage
+// over, move on to the next stage.  `mine` false: the half belongs to the other warp of the pair.
+template <int B, int GS, bool BF16, int H>
+__device__ __forceinline__ bool tc_producer_half(TcProducer &pr, bool mine, bool valid, int lane, const uint32_t (&w)[2 * B],
+                                                 const uint16_t (&slo)[TcScales<GS>::NG],
+                                                 const uint16_t (&shi)[TcScales<GS>::NG]) {
+  if (mine) {
+    if (!mbar_wait(pr.bar_empty + pr.idx8, pr.parity)) return false;  // the tensor pipe is done with what this stage held
+    if (valid) tc_store_half<B, GS, BF16, H>(w, slo, shi, pr.a_lane + pr.off);
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy stores -> tensor pipe reads
+    __syncwarp();
+    if (lane == 0) mbar_arrive(pr.bar_full + pr.idx8);
+  }
+  pr.off += pr.stage_bytes;
+  pr.idx8 += 8;
+  if (pr.idx8 == pr.stages8) {
+    pr.off = 0;
+    pr.idx8 = 0;
+    pr.parity ^= 1;
+  }
+  return true;
+}
+
 // PW producer warps: 8 (each decodes both 64-wide halves of its blocks; two CTAs share an SM) or 16 (warps w and
 // w + 8 share a row tile and take one half each, so that a CTA that has the SM to itself overlaps the latency of
 // one stage with the work of the next).
@@ -259,60 +322,28 @@ __global__ void __launch_bounds__((PW + 2) * 32, PW == 8 ? 2 : 1) gemm_tc_kernel
     for (int a = 0; a < kAhead; ++a)
       if (valid && a < nblk) load_next(wq[a], sq_lo[a], sq_hi[a]);
 
-    const uint32_t ring_bytes = static_cast<uint32_t>(stages) * plan.stage_bytes;
-    // this lane's 16 bytes of rows g and g+8 in the A tile of stage 0, chunk t
-    unsigned char *a_lane = base + plan.off_stages + plan.b_stage_bytes + t * kTcChunkStride + (2 * ptile) * 128 + g * 16;
-    uint32_t cur_stage_off = 0, cur_bar = bar_full, cur_empty = bar_empty, cur_parity = 1;
-    int blocks_left = nblk, loads_left = nblk - kAhead;
-    while (blocks_left > 0 && !failed) {
+    // this lane's 16 bytes of rows g and g+8 in the A tile of stage 0, chunk t (shared-memory address)
+    const uint32_t a_lane = base_u32 + plan.off_stages + plan.b_stage_bytes + t * kTcChunkStride + (2 * ptile) * 128 + g * 16;
+    const uint32_t stages8 = static_cast<uint32_t>(stages) * 8;
+    TcProducer pr;  // the stage the next half block goes to, and what does not change
+    pr.off = 0;
+    pr.idx8 = 0;
+    pr.parity = 1;
+    pr.stage_bytes = plan.stage_bytes;
+    pr.stages8 = stages8;
+    pr.bar_full = bar_full;
+    pr.bar_empty = bar_empty;
+    pr.a_lane = a_lane;
+    for (int blk = 0; blk < nblk && !failed; blk += kAhead) {
 #pragma unroll
       for (int a = 0; a < kAhead; ++a) {
-        if (blocks_left > 0 && !failed) {
-#pragma unroll
-          for (int h = 0; h < 2; ++h) {
-            if (PW == 8 || h == my_half) {
-            if (!mbar_wait(cur_empty, cur_parity)) {  // the tensor pipe is done with what this stage held
-              failed = true;
-              break;
-            }
-            if (valid) {
-              // dense weights of this lane: rows g and g+8, two 16-byte chunks per row
-#pragma unroll
-              for (int jj = 2 * h; jj < 2 * h + 2; ++jj) {
-                const int gi = (GS == 32) ? jj : 0;
-                const uint32_t s_lo = dense_scale<B, BF16>(sq_lo[a][gi]), s_hi = dense_scale<B, BF16>(sq_hi[a][gi]);
-                uint4 lo, hi;
-                lo.x = dense_pair<B, BF16>(wq[a], 8 * jj + 0, s_lo);
-                lo.y = dense_pair<B, BF16>(wq[a], 8 * jj + 2, s_lo);
-                lo.z = dense_pair<B, BF16>(wq[a], 8 * jj + 4, s_lo);
-                lo.w = dense_pair<B, BF16>(wq[a], 8 * jj + 6, s_lo);
-                hi.x = dense_pair<B, BF16>(wq[a], 8 * jj + 1, s_hi);
-                hi.y = dense_pair<B, BF16>(wq[a], 8 * jj + 3, s_hi);
-                hi.z = dense_pair<B, BF16>(wq[a], 8 * jj + 5, s_hi);
-                hi.w = dense_pair<B, BF16>(wq[a], 8 * jj + 7, s_hi);
-                unsigned char *dst = a_lane + cur_stage_off + (jj & 1) * (4 * kTcChunkStride);
-                *reinterpret_cast<uint4 *>(dst) = lo;
-                *reinterpret_cast<uint4 *>(dst + 128) = hi;
-              }
-            }
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy stores -> tensor pipe reads
-            __syncwarp();
-            if (lane == 0) mbar_arrive(cur_bar);
-            }
-            cur_stage_off += plan.stage_bytes;
-            cur_bar += 8;
-            cur_empty += 8;
-            if (cur_stage_off == ring_bytes) {
-              cur_stage_off = 0;
-              cur_bar = bar_full;
-              cur_empty = bar_empty;
-              cur_parity ^= 1;
-            }
+        if (blk + a < nblk && !failed) {
+          if (!tc_producer_half<B, GS, BF16, 0>(pr, PW == 8 || my_half == 0, valid, lane, wq[a], sq_lo[a], sq_hi[a]) ||
+              !tc_producer_half<B, GS, BF16, 1>(pr, PW == 8 || my_half == 1, valid, lane, wq[a], sq_lo[a], sq_hi[a])) {
+            failed = true;
+          } else if (valid && blk + a + kAhead < nblk) {
+            load_next(wq[a], sq_lo[a], sq_hi[a]);  // this block's registers are free: fetch the block kAhead ahead
           }
-          // this block's registers are free: fetch the block kAhead ahead
-          if (valid && loads_left > 0) load_next(wq[a], sq_lo[a], sq_hi[a]);
-          --loads_left;
-          --blocks_left;
         }
       }
     }
