@@ -150,13 +150,16 @@ int matgptq_b200_matmul_grouped(const matgptq_b200_segment *segments, int n_segm
   const bool bf16 = (flags & MATGPTQ_B200_FLAG_BF16) != 0;
   const bool pdl = (flags & MATGPTQ_B200_FLAG_PDL) != 0;
   int r = MG_ERR_UNSUPPORTED;
+  mg::GroupedSegment segs[8];
+  for (int i = 0; i < n_segments; ++i)
+    segs[i] = mg::GroupedSegment{segments[i].w, segments[i].s, static_cast<int>(segments[i].n_out),
+                                 static_cast<int>(segments[i].bitwidth)};
   if (batch < kTensorCoreMinBatch) {
-    mg::GroupedSegment segs[8];
-    for (int i = 0; i < n_segments; ++i)
-      segs[i] = mg::GroupedSegment{segments[i].w, segments[i].s, static_cast<int>(segments[i].n_out),
-                                   static_cast<int>(segments[i].bitwidth)};
     r = mg::gemv_grouped_launch(segs, n_segments, static_cast<int>(group_size), static_cast<int>(n_in),
                                 static_cast<int>(batch), x, y, static_cast<int>(total), bf16, pdl, cs);
+  } else if (!(flags & MATGPTQ_B200_FLAG_SCRATCH_REDUCE)) {
+    r = mg::gemm_tc_grouped_launch(segs, n_segments, static_cast<int>(group_size), static_cast<int>(n_in),
+                                   static_cast<int>(batch), x, y, static_cast<int>(total), bf16, pdl, cs);
   }
   if (r == MG_ERR_UNSUPPORTED) {
     // one launch per segment into its column block: the tensor-core path, or segments that cannot share a launch shape

@@ -240,7 +240,7 @@ __device__ __forceinline__ bool tc_producer_half(TcProducer &pr, bool mine, bool
 // w + 8 share a row tile and take one half each, so that a CTA that has the SM to itself overlaps the latency of
 // one stage with the work of the next).
 template <int B, int GS, bool BF16, int PW>
-__global__ void __launch_bounds__((PW + 2) * 32, PW == 8 ? 2 : 1) gemm_tc_kernel(const GemmParams p, const __grid_constant__ CUtensorMap xmap) {
+__device__ __forceinline__ void gemm_tc_body(const GemmParams &p, const CUtensorMap &xmap, const int tile128) {
   extern __shared__ unsigned char tc_smem_raw[];
   const uint32_t raw_u32 = smem_u32(tc_smem_raw);
   const uint32_t base_u32 = (raw_u32 + 1023u) & ~1023u;
@@ -255,7 +255,7 @@ __global__ void __launch_bounds__((PW + 2) * 32, PW == 8 ? 2 : 1) gemm_tc_kernel
   const uint32_t bar_done = base_u32 + 16 * 8;
   volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(base + 17 * 8);
 
-  const int tile128 = blockIdx.x, sk = blockIdx.y;
+  const int sk = blockIdx.y;
   const int m0 = blockIdx.z * 256;
   const int mrows = min(p.M - m0, 256);
   const int kb_lo = sk * p.kblocks / p.split;
@@ -481,6 +481,47 @@ __global__ void __launch_bounds__((PW + 2) * 32, PW == 8 ? 2 : 1) gemm_tc_kernel
   }
 }
 
+template <int B, int GS, bool BF16, int PW>
+__global__ void __launch_bounds__((PW + 2) * 32, PW == 8 ? 2 : 1) gemm_tc_kernel(const GemmParams p, const __grid_constant__ CUtensorMap xmap) {
+  gemm_tc_body<B, GS, BF16, PW>(p, xmap, static_cast<int>(blockIdx.x));
+}
+
+// Several layers that read the same activations (q, k, v; gate and up), each with its own bitwidth, in ONE launch:
+// blockIdx.x counts the 128-row tiles of all segments; a CTA looks its segment up and runs the body of that
+// bitwidth on the segment's column block of y.
+constexpr int kTcMaxSegments = 8;
+struct GemmGroupedParams {
+  GemmParams common;  // x, K, M, ldy, kblocks, split, ncols, stages; w, s, y and N are per segment
+  const uint32_t *w[kTcMaxSegments];
+  const uint16_t *s[kTcMaxSegments];
+  int n_out[kTcMaxSegments];
+  int col0[kTcMaxSegments];       // first column of the segment in y
+  int tile_end[kTcMaxSegments];   // running count of 128-row tiles up to and including the segment
+  int bits[kTcMaxSegments];
+  int nseg;
+};
+
+template <int GS, bool BF16, int PW>
+__global__ void __launch_bounds__((PW + 2) * 32, PW == 8 ? 2 : 1)
+    gemm_tc_grouped_kernel(const __grid_constant__ GemmGroupedParams gp, const __grid_constant__ CUtensorMap xmap) {
+  int seg = 0;
+  const int bx = static_cast<int>(blockIdx.x);
+  while (seg + 1 < gp.nseg && bx >= gp.tile_end[seg]) ++seg;
+  GemmParams p = gp.common;
+  p.w = gp.w[seg];
+  p.s = gp.s[seg];
+  p.N = gp.n_out[seg];
+  p.y = gp.common.y + gp.col0[seg];
+  const int tile = bx - (seg ? gp.tile_end[seg - 1] : 0);
+  switch (gp.bits[seg]) {
+    case 2: gemm_tc_body<2, GS, BF16, PW>(p, xmap, tile); break;
+    case 3: gemm_tc_body<3, GS, BF16, PW>(p, xmap, tile); break;
+    case 4: gemm_tc_body<4, GS, BF16, PW>(p, xmap, tile); break;
+    case 6: gemm_tc_body<6, GS, BF16, PW>(p, xmap, tile); break;
+    default: gemm_tc_body<8, GS, BF16, PW>(p, xmap, tile); break;
+  }
+}
+
 // partial[split][M][N] fp32 -> y[M][N] (rows ldy elements apart), added in the order of the K ranges: the second
 // kernel of a K split that goes through scratch memory
 template <bool BF16>
@@ -551,17 +592,24 @@ static int make_x_tensor_map(CUtensorMap *map, const void *x, int M, int K, int 
   return r == CUDA_SUCCESS ? MG_OK : MG_ERR_CUDA;
 }
 
+// As many pipeline stages as fit: in half of the SM's shared memory with 8 producer warps (two CTAs per SM), in
+// all of it with 16.
+static int tc_pick_stages(int ncols, int producer_warps) {
+  int stages = 8;
+  if (producer_warps == 8) {
+    while (stages > 3 && tc_plan(ncols, stages).total > kTcHalfSmBytes) --stages;
+  } else {
+    while (stages > 2 && tc_plan(ncols, stages).total > 2 * kTcHalfSmBytes) --stages;
+  }
+  return stages;
+}
+
 template <int B, int GS, bool BF16, int PW>
 static int launch_gemm_tc_warps(GemmParams p, cudaStream_t stream, bool pdl, float *fallback_partial) {
   auto kernel = gemm_tc_kernel<B, GS, BF16, PW>;
   CUtensorMap xmap;
   if (make_x_tensor_map(&xmap, p.x, p.M, p.K, p.ncols) != MG_OK) return MG_ERR_CUDA;
-  int stages = 8;
-  if (PW == 8) {
-    while (stages > 3 && tc_plan(p.ncols, stages).total > kTcHalfSmBytes) --stages;
-  } else {
-    while (stages > 2 && tc_plan(p.ncols, stages).total > 2 * kTcHalfSmBytes) --stages;
-  }
+  const int stages = tc_pick_stages(p.ncols, PW);
   p.stages = stages;
   const TcPlan plan = tc_plan(p.ncols, stages);
   static SharedMemoryOptIn opt_in;  // one per instantiation of this launcher
@@ -649,6 +697,103 @@ static int launch_gemm_tc_group(const GemmParams &p, int group_size, bool bf16, 
     case 128: return launch_gemm_tc_type<B, 128>(p, bf16, stream, pdl, fb);
     default: return MG_ERR_BAD_ARG;
   }
+}
+
+template <int GS, bool BF16, int PW>
+static int launch_gemm_tc_grouped_warps(GemmGroupedParams gp, int total_tiles, cudaStream_t stream, bool pdl) {
+  auto kernel = gemm_tc_grouped_kernel<GS, BF16, PW>;
+  GemmParams &p = gp.common;
+  CUtensorMap xmap;
+  if (make_x_tensor_map(&xmap, p.x, p.M, p.K, p.ncols) != MG_OK) return MG_ERR_CUDA;
+  p.stages = tc_pick_stages(p.ncols, PW);
+  const TcPlan plan = tc_plan(p.ncols, p.stages);
+  static SharedMemoryOptIn opt_in;  // one per instantiation of this launcher
+  {
+    const int st = opt_in.ensure(kernel, 224 * 1024);
+    if (st != MG_OK) return st;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(total_tiles, p.split, (p.M + 255) / 256);
+  cfg.blockDim = dim3((PW + 2) * 32, 1, 1);
+  cfg.dynamicSmemBytes = plan.total;
+  cfg.stream = stream;
+  cudaLaunchAttribute attrs[2];
+  int na = 0;
+  if (pdl) {
+    attrs[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attrs[na].val.programmaticStreamSerializationAllowed = 1;
+    ++na;
+  }
+  if (p.split > 1) {
+    attrs[na].id = cudaLaunchAttributeClusterDimension;
+    attrs[na].val.clusterDim.x = 1;
+    attrs[na].val.clusterDim.y = static_cast<unsigned>(p.split);
+    attrs[na].val.clusterDim.z = 1;
+    ++na;
+  }
+  cfg.attrs = attrs;
+  cfg.numAttrs = na;
+  if (cudaLaunchKernelEx(&cfg, kernel, gp, xmap) != cudaSuccess) {
+    (void)cudaGetLastError();
+    return MG_ERR_UNSUPPORTED;  // the caller launches segment by segment (which can fall back to scratch)
+  }
+  return MG_OK;
+}
+
+// One launch for several segments (group size 128, no zero points); MG_ERR_UNSUPPORTED tells the caller to launch
+// them one by one.
+int gemm_tc_grouped_launch(const GroupedSegment *segments, int nseg, int group_size, int K, int M, const void *x, void *y,
+                           int ldy, bool bf16, bool pdl, cudaStream_t stream) {
+  if (group_size != 128 || nseg < 2 || nseg > kTcMaxSegments) return MG_ERR_UNSUPPORTED;
+  int sm_count = 0;
+  {
+    const int st = current_device_sm_count(&sm_count);
+    if (st != MG_OK) return st;
+  }
+  {
+    // Worth it when the segments together fill the GPU without a K split (gate and up of Llama-3.1-8B at 128 rows:
+    // 44.6 us in one launch against 59.4 in two); a few small segments (q, k, v: 48 tiles) gain nothing over
+    // launches that overlap through programmatic dependent launch (25.0 against 24.1 us at 64 rows).
+    int all_tiles = 0;
+    for (int i = 0; i < nseg; ++i) all_tiles += (segments[i].n_out + 127) / 128;
+    if (2 * all_tiles < sm_count) return MG_ERR_UNSUPPORTED;
+  }
+  GemmGroupedParams gp = {};
+  int tiles = 0, col = 0;
+  for (int i = 0; i < nseg; ++i) {
+    gp.w[i] = static_cast<const uint32_t *>(segments[i].w);
+    gp.s[i] = static_cast<const uint16_t *>(segments[i].s);
+    gp.n_out[i] = segments[i].n_out;
+    gp.bits[i] = segments[i].bitwidth;
+    gp.col0[i] = col;
+    col += segments[i].n_out;
+    tiles += (segments[i].n_out + 127) / 128;
+    gp.tile_end[i] = tiles;
+  }
+  gp.nseg = nseg;
+  GemmParams &p = gp.common;
+  p.w = nullptr;
+  p.s = nullptr;
+  p.x = static_cast<const uint16_t *>(x);
+  p.y = static_cast<uint16_t *>(y);
+  p.N = 0;
+  p.K = K;
+  p.M = M;
+  p.ldy = ldy;
+  p.kblocks = K / 128;
+  p.partial = nullptr;
+  p.split = gemm_tc_pick_split(tiles * 128, K, M, sm_count);
+  if (p.split > p.kblocks) p.split = p.kblocks;
+  p.ncols = round_up16(M < 256 ? M : 256);
+  p.stages = 0;
+  const long long ctas = static_cast<long long>(tiles) * p.split * ((M + 255) / 256);
+  const bool sixteen = !tc_two_ctas_per_sm(p.ncols) || ctas <= sm_count;
+  if (bf16) {
+    return sixteen ? launch_gemm_tc_grouped_warps<128, true, 16>(gp, tiles, stream, pdl)
+                   : launch_gemm_tc_grouped_warps<128, true, 8>(gp, tiles, stream, pdl);
+  }
+  return sixteen ? launch_gemm_tc_grouped_warps<128, false, 16>(gp, tiles, stream, pdl)
+                 : launch_gemm_tc_grouped_warps<128, false, 8>(gp, tiles, stream, pdl);
 }
 
 // workspace: fp32 scratch of at least gemm_tc_workspace_bytes() or null.  The sums of a split K meet inside a

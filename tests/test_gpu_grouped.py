@@ -25,7 +25,7 @@ def _segments(rows_bits, n_in, gs, dtype, cuda, seed=0):
 
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
 @pytest.mark.parametrize("gs", [-1, 32, 128])
-@pytest.mark.parametrize("m", [1, 5, 16, 23, 40])
+@pytest.mark.parametrize("m", [1, 5, 16, 23, 40, 130, 300])
 def test_mixed_bitwidth_segments(cuda, dtype, gs, m):
     from matgptq_b200 import _native
     rows_bits = [(64, 2), (208, 3), (16, 4), (96, 6), (48, 8)]  # every bitwidth, ragged row counts
@@ -45,7 +45,7 @@ def test_mixed_bitwidth_segments(cuda, dtype, gs, m):
         col += rows
 
 
-@pytest.mark.parametrize("m", [1, 8, 16])
+@pytest.mark.parametrize("m", [1, 8, 16, 32, 100])  # from 32 rows: one grouped launch of the tensor-core path
 @pytest.mark.parametrize("layer", ["qkv", "gate_up"])
 def test_llama_fused_layers(cuda, layer, m):
     """The two fused layers of the Llama-3.1-8B architecture with the bitwidths a mean-3-bit assignment gives them."""
