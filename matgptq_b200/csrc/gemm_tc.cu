@@ -134,9 +134,9 @@ __device__ __forceinline__ uint32_t map_to_cta(uint32_t addr, int cta) {
   return r;
 }
 
-__device__ __forceinline__ float ld_cluster_f32(uint32_t addr) {
-  float v;
-  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(addr) : "memory");
+__device__ __forceinline__ float4 ld_cluster_f32x4(uint32_t addr) {
+  float4 v;
+  asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(addr));
   return v;
 }
 
@@ -460,14 +460,36 @@ __device__ __forceinline__ void gemm_tc_body(const GemmParams &p, const CUtensor
     if (warp < PW) {
       const int per = (p.ncols + p.split - 1) / p.split;
       const int c_lo = sk * per, c_hi = min(c_lo + per, p.ncols);
-      for (int idx = tid; idx < (c_hi - c_lo) * 128; idx += PW * 32) {
-        const int c = c_lo + (idx >> 7), nn = idx & 127;
+      // Four out-features of one batch row per thread and step, two CTAs' values in flight at a time.  Measured on
+      // B200: scalar loads one after the other cost gate/up at 128 rows (two CTAs along K, 64 batch rows each) 9 us
+      // in this loop; with all of a thread's loads in flight at once that drops to 4 us, but clusters of eight then
+      // lose ~1 us (q/o, k/v at 32 rows), so the loads go out in pairs.
+      for (int idx = tid; idx < (c_hi - c_lo) * 32; idx += PW * 32) {
+        const int c = c_lo + (idx >> 5), nn = (idx & 31) * 4;
         const int m = m0 + c, n = tile128 * 128 + nn;
         if (m < m0 + mrows && n < p.N) {
           const uint32_t local = smem_u32(staging + c * 128 + nn);
-          float sum = 0.f;
-          for (int s = 0; s < p.split; ++s) sum += ld_cluster_f32(map_to_cta(local, s));
-          p.y[static_cast<size_t>(m) * p.ldy + n] = to_out16<BF16>(sum);
+          float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
+          for (int s = 0; s < p.split; s += 2) {
+            const float4 a = ld_cluster_f32x4(map_to_cta(local, s));
+            float4 b = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (s + 1 < p.split) b = ld_cluster_f32x4(map_to_cta(local, s + 1));
+            sum.x = (sum.x + a.x) + b.x;
+            sum.y = (sum.y + a.y) + b.y;
+            sum.z = (sum.z + a.z) + b.z;
+            sum.w = (sum.w + a.w) + b.w;
+          }
+          uint16_t *dst = p.y + static_cast<size_t>(m) * p.ldy + n;
+          const uint16_t o0 = to_out16<BF16>(sum.x), o1 = to_out16<BF16>(sum.y), o2 = to_out16<BF16>(sum.z),
+                         o3 = to_out16<BF16>(sum.w);
+          if (n + 3 < p.N && (reinterpret_cast<uintptr_t>(dst) & 7u) == 0) {
+            *reinterpret_cast<uint2 *>(dst) = make_uint2(o0 | (static_cast<uint32_t>(o1) << 16), o2 | (static_cast<uint32_t>(o3) << 16));
+          } else {
+            dst[0] = o0;
+            if (n + 1 < p.N) dst[1] = o1;
+            if (n + 2 < p.N) dst[2] = o2;
+            if (n + 3 < p.N) dst[3] = o3;
+          }
         }
       }
     }
@@ -484,42 +506,6 @@ __device__ __forceinline__ void gemm_tc_body(const GemmParams &p, const CUtensor
 template <int B, int GS, bool BF16, int PW>
 __global__ void __launch_bounds__((PW + 2) * 32, PW == 8 ? 2 : 1) gemm_tc_kernel(const GemmParams p, const __grid_constant__ CUtensorMap xmap) {
   gemm_tc_body<B, GS, BF16, PW>(p, xmap, static_cast<int>(blockIdx.x));
-}
-
-// Several layers that read the same activations (q, k, v; gate and up), each with its own bitwidth, in ONE launch:
-// blockIdx.x counts the 128-row tiles of all segments; a CTA looks its segment up and runs the body of that
-// bitwidth on the segment's column block of y.
-constexpr int kTcMaxSegments = 8;
-struct GemmGroupedParams {
-  GemmParams common;  // x, K, M, ldy, kblocks, split, ncols, stages; w, s, y and N are per segment
-  const uint32_t *w[kTcMaxSegments];
-  const uint16_t *s[kTcMaxSegments];
-  int n_out[kTcMaxSegments];
-  int col0[kTcMaxSegments];       // first column of the segment in y
-  int tile_end[kTcMaxSegments];   // running count of 128-row tiles up to and including the segment
-  int bits[kTcMaxSegments];
-  int nseg;
-};
-
-template <int GS, bool BF16, int PW>
-__global__ void __launch_bounds__((PW + 2) * 32, PW == 8 ? 2 : 1)
-    gemm_tc_grouped_kernel(const __grid_constant__ GemmGroupedParams gp, const __grid_constant__ CUtensorMap xmap) {
-  int seg = 0;
-  const int bx = static_cast<int>(blockIdx.x);
-  while (seg + 1 < gp.nseg && bx >= gp.tile_end[seg]) ++seg;
-  GemmParams p = gp.common;
-  p.w = gp.w[seg];
-  p.s = gp.s[seg];
-  p.N = gp.n_out[seg];
-  p.y = gp.common.y + gp.col0[seg];
-  const int tile = bx - (seg ? gp.tile_end[seg - 1] : 0);
-  switch (gp.bits[seg]) {
-    case 2: gemm_tc_body<2, GS, BF16, PW>(p, xmap, tile); break;
-    case 3: gemm_tc_body<3, GS, BF16, PW>(p, xmap, tile); break;
-    case 4: gemm_tc_body<4, GS, BF16, PW>(p, xmap, tile); break;
-    case 6: gemm_tc_body<6, GS, BF16, PW>(p, xmap, tile); break;
-    default: gemm_tc_body<8, GS, BF16, PW>(p, xmap, tile); break;
-  }
 }
 
 // partial[split][M][N] fp32 -> y[M][N] (rows ldy elements apart), added in the order of the K ranges: the second
@@ -697,103 +683,6 @@ static int launch_gemm_tc_group(const GemmParams &p, int group_size, bool bf16, 
     case 128: return launch_gemm_tc_type<B, 128>(p, bf16, stream, pdl, fb);
     default: return MG_ERR_BAD_ARG;
   }
-}
-
-template <int GS, bool BF16, int PW>
-static int launch_gemm_tc_grouped_warps(GemmGroupedParams gp, int total_tiles, cudaStream_t stream, bool pdl) {
-  auto kernel = gemm_tc_grouped_kernel<GS, BF16, PW>;
-  GemmParams &p = gp.common;
-  CUtensorMap xmap;
-  if (make_x_tensor_map(&xmap, p.x, p.M, p.K, p.ncols) != MG_OK) return MG_ERR_CUDA;
-  p.stages = tc_pick_stages(p.ncols, PW);
-  const TcPlan plan = tc_plan(p.ncols, p.stages);
-  static SharedMemoryOptIn opt_in;  // one per instantiation of this launcher
-  {
-    const int st = opt_in.ensure(kernel, 224 * 1024);
-    if (st != MG_OK) return st;
-  }
-  cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(total_tiles, p.split, (p.M + 255) / 256);
-  cfg.blockDim = dim3((PW + 2) * 32, 1, 1);
-  cfg.dynamicSmemBytes = plan.total;
-  cfg.stream = stream;
-  cudaLaunchAttribute attrs[2];
-  int na = 0;
-  if (pdl) {
-    attrs[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attrs[na].val.programmaticStreamSerializationAllowed = 1;
-    ++na;
-  }
-  if (p.split > 1) {
-    attrs[na].id = cudaLaunchAttributeClusterDimension;
-    attrs[na].val.clusterDim.x = 1;
-    attrs[na].val.clusterDim.y = static_cast<unsigned>(p.split);
-    attrs[na].val.clusterDim.z = 1;
-    ++na;
-  }
-  cfg.attrs = attrs;
-  cfg.numAttrs = na;
-  if (cudaLaunchKernelEx(&cfg, kernel, gp, xmap) != cudaSuccess) {
-    (void)cudaGetLastError();
-    return MG_ERR_UNSUPPORTED;  // the caller launches segment by segment (which can fall back to scratch)
-  }
-  return MG_OK;
-}
-
-// One launch for several segments (group size 128, no zero points); MG_ERR_UNSUPPORTED tells the caller to launch
-// them one by one.
-int gemm_tc_grouped_launch(const GroupedSegment *segments, int nseg, int group_size, int K, int M, const void *x, void *y,
-                           int ldy, bool bf16, bool pdl, cudaStream_t stream) {
-  if (group_size != 128 || nseg < 2 || nseg > kTcMaxSegments) return MG_ERR_UNSUPPORTED;
-  int sm_count = 0;
-  {
-    const int st = current_device_sm_count(&sm_count);
-    if (st != MG_OK) return st;
-  }
-  {
-    // Worth it when the segments together fill the GPU without a K split (gate and up of Llama-3.1-8B at 128 rows:
-    // 44.6 us in one launch against 59.4 in two); a few small segments (q, k, v: 48 tiles) gain nothing over
-    // launches that overlap through programmatic dependent launch (25.0 against 24.1 us at 64 rows).
-    int all_tiles = 0;
-    for (int i = 0; i < nseg; ++i) all_tiles += (segments[i].n_out + 127) / 128;
-    if (2 * all_tiles < sm_count) return MG_ERR_UNSUPPORTED;
-  }
-  GemmGroupedParams gp = {};
-  int tiles = 0, col = 0;
-  for (int i = 0; i < nseg; ++i) {
-    gp.w[i] = static_cast<const uint32_t *>(segments[i].w);
-    gp.s[i] = static_cast<const uint16_t *>(segments[i].s);
-    gp.n_out[i] = segments[i].n_out;
-    gp.bits[i] = segments[i].bitwidth;
-    gp.col0[i] = col;
-    col += segments[i].n_out;
-    tiles += (segments[i].n_out + 127) / 128;
-    gp.tile_end[i] = tiles;
-  }
-  gp.nseg = nseg;
-  GemmParams &p = gp.common;
-  p.w = nullptr;
-  p.s = nullptr;
-  p.x = static_cast<const uint16_t *>(x);
-  p.y = static_cast<uint16_t *>(y);
-  p.N = 0;
-  p.K = K;
-  p.M = M;
-  p.ldy = ldy;
-  p.kblocks = K / 128;
-  p.partial = nullptr;
-  p.split = gemm_tc_pick_split(tiles * 128, K, M, sm_count);
-  if (p.split > p.kblocks) p.split = p.kblocks;
-  p.ncols = round_up16(M < 256 ? M : 256);
-  p.stages = 0;
-  const long long ctas = static_cast<long long>(tiles) * p.split * ((M + 255) / 256);
-  const bool sixteen = !tc_two_ctas_per_sm(p.ncols) || ctas <= sm_count;
-  if (bf16) {
-    return sixteen ? launch_gemm_tc_grouped_warps<128, true, 16>(gp, tiles, stream, pdl)
-                   : launch_gemm_tc_grouped_warps<128, true, 8>(gp, tiles, stream, pdl);
-  }
-  return sixteen ? launch_gemm_tc_grouped_warps<128, false, 16>(gp, tiles, stream, pdl)
-                 : launch_gemm_tc_grouped_warps<128, false, 8>(gp, tiles, stream, pdl);
 }
 
 // workspace: fp32 scratch of at least gemm_tc_workspace_bytes() or null.  The sums of a split K meet inside a

@@ -62,8 +62,6 @@ long long gemm_tc_workspace_bytes(int N, int K, int M, int sm_count);
 int gemm_tc_launch(int bitwidth, int group_size, int N, int K, int M, const void *w, const void *s, const void *x,
                    void *y, void *workspace, long long workspace_bytes, bool bf16, bool pdl, int split_override,
                    cudaStream_t stream, int ldy = 0, bool scratch_reduce = false);
-int gemm_tc_grouped_launch(const GroupedSegment *segments, int nseg, int group_size, int K, int M, const void *x, void *y,
-                           int ldy, bool bf16, bool pdl, cudaStream_t stream);
 int gemm_tc_device_status(int *status_out, int reset);
 
 // selftest.cu
