@@ -237,12 +237,23 @@ template <int B, int P_OFF> __device__ __forceinline__ uint32_t dense_int_bf16_a
 // conversions): the field is isolated inside the 7 mantissa bits of bfloat16 with the exponent of 128 OR-ed in by
 // the same LOP3 (value 128 + code * 2^p), and one bfloat16 fma makes the integer.  Needs code * 2^p < 128, i.e.
 // the field shifted down to bit 0 first where it sits higher (every 4-bit field but the lowest, the third offset of
-// 3-bit codes); 8-bit codes do not fit 7 mantissa bits and keep the fp16 route.
+// 3-bit codes); 8-bit codes go in as two fields.
 template <int B> __device__ __forceinline__ uint32_t dense_int_bf16(const uint32_t (&w)[2 * B], int P) {
-  static_assert(B != 8, "8-bit codes need 8 mantissa bits");
   constexpr uint32_t kMagicBf = 0x43004300u;  // bfloat162(128, 128)
   const int i = P >> 2, r = P & 3;
-  if constexpr (B == 4) {
+  if constexpr (B == 8) {
+    // Eight bits do not fit the 7 mantissa bits, so the code goes in as two fields: the low seven bits under the
+    // magic (t = 128 + low) and the top bit on the exponent's lowest bit (q = 128 or 256).  Then
+    // code - 128 = t + (q - 384), two bfloat16 additions whose results are exact (-256 or -128, then -128..127).
+    const uint32_t W = w[4 * (i >> 1) + r] >> (8 * (i & 1));
+    const uint32_t t = lop3_and_or(W, 0x007F007Fu, kMagicBf);
+    const uint32_t q = lop3_and_or(W, 0x00800080u, kMagicBf);
+    constexpr uint32_t k384 = bf162_const(-384.0f);
+    const __nv_bfloat162 u = __hadd2(*reinterpret_cast<const __nv_bfloat162 *>(&q), *reinterpret_cast<const __nv_bfloat162 *>(&k384));
+    const __nv_bfloat162 v = __hadd2(*reinterpret_cast<const __nv_bfloat162 *>(&t), u);
+    static_assert(DensePre<8>::value == 1, "8-bit codes are used as they are");
+    return *reinterpret_cast<const uint32_t *>(&v);
+  } else if constexpr (B == 4) {
     const uint32_t W = w[4 * (i >> 2) + r] >> (4 * (i & 3));
     return dense_int_bf16_at<4, 0>(lop3_and_or(W, 0x000F000Fu, kMagicBf));
   } else if constexpr (B == 3) {
@@ -264,7 +275,7 @@ template <int B> __device__ __forceinline__ uint32_t dense_int_bf16(const uint32
 // scale2: dense_scale() of the row's scale
 template <int B, bool BF16>
 __device__ __forceinline__ uint32_t dense_pair(const uint32_t (&w)[2 * B], int P, uint32_t scale2) {
-  if constexpr (BF16 && B != 8) {
+  if constexpr (BF16) {
     const uint32_t vb = dense_int_bf16<B>(w, P);
     const __nv_bfloat162 r = __hmul2(*reinterpret_cast<const __nv_bfloat162 *>(&scale2), *reinterpret_cast<const __nv_bfloat162 *>(&vb));
     return *reinterpret_cast<const uint32_t *>(&r);
@@ -279,13 +290,7 @@ __device__ __forceinline__ uint32_t dense_pair(const uint32_t (&w)[2 * B], int P
     case 6: v = dense_int_at<B, 6>(x); break;
     default: v = dense_int_at<B, 8>(x); break;
   }
-  if constexpr (BF16) {
-    const uint32_t vb = h2_to_bf2(v);
-    const __nv_bfloat162 r = __hmul2(*reinterpret_cast<const __nv_bfloat162 *>(&scale2), *reinterpret_cast<const __nv_bfloat162 *>(&vb));
-    return *reinterpret_cast<const uint32_t *>(&r);
-  } else {
-    return h2_bits(__hmul2(bits_h2(scale2), bits_h2(v)));
-  }
+  return h2_bits(__hmul2(bits_h2(scale2), bits_h2(v)));
 }
 
 // Coalesced load of a lane's words of one block (all lanes of a warp call it).
