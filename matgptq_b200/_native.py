@@ -13,6 +13,7 @@ _LIB_PATH = os.environ.get("MATGPTQ_B200_LIBRARY") or os.path.join(
     os.path.dirname(os.path.abspath(__file__)), "libmatgptq_b200.so")
 
 OK = 0
+ERR_CUDA = 2  # MATGPTQ_B200_ERR_CUDA: a CUDA runtime call or a kernel launch failed
 FLAG_ASYNC = 1
 FLAG_BF16 = 2
 FLAG_PDL = 4

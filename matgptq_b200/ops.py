@@ -165,6 +165,40 @@ def _check_matmul_args(input, matgptq_weights, matgptq_scales, n_out_features, n
         raise RuntimeError("input must have shape [..., M, n_in_features]")
 
 
+def _launch_matmul(what: str, dev, bitwidth: int, group_size: int, n_out_features: int, n_in_features: int, batch: int,
+                   weights: torch.Tensor, scales: torch.Tensor, x: torch.Tensor, out: torch.Tensor, feature_flag: int) -> None:
+    """One call of the C-ABI product.  Scratch is only allocated when it is used: with FLAG_SCRATCH_REDUCE, or for
+    the second attempt on a device that could not place the thread-block cluster of a split K."""
+    def call(ws):
+        return _lib.matgptq_b200_matmul_ws(bitwidth, group_size, n_out_features, n_in_features, batch,
+                                           weights.data_ptr(), scales.data_ptr(), x.data_ptr(), out.data_ptr(),
+                                           _stream_ptr(dev), feature_flag,
+                                           ws.data_ptr() if ws is not None else None, ws.numel() if ws is not None else 0, 0, 0)
+
+    def scratch():
+        need = _lib.matgptq_b200_matmul_workspace_bytes(n_out_features, n_in_features, batch)
+        return torch.empty(need, dtype=torch.uint8, device=dev) if need > 0 else None
+
+    st = call(scratch() if feature_flag & _native.FLAG_SCRATCH_REDUCE else None)
+    if st == _native.ERR_CUDA and not feature_flag & _native.FLAG_SCRATCH_REDUCE:
+        ws = scratch()
+        if ws is not None:
+            st = call(ws)
+    _native.check(st, what)
+
+
+def _prepare_input(input: torch.Tensor, batch: int, n_in_features: int) -> torch.Tensor:
+    x = input
+    if input.dim() > 2:
+        # the reference reads the last two dimensions only (csrc/bindings.cpp:171)
+        x = input.reshape(-1, batch, n_in_features)[0]
+    if not x.is_contiguous():
+        x = x.contiguous()
+    if x.data_ptr() % 16 != 0:
+        x = x.clone()
+    return x
+
+
 def _matmul_impl(input: torch.Tensor, matgptq_weights: torch.Tensor, matgptq_scales: torch.Tensor, n_out_features: int,
                  n_in_features: int, bitwidth: int, group_size: int, feature_flag: int) -> torch.Tensor:
     _check_matmul_args(input, matgptq_weights, matgptq_scales, n_out_features, n_in_features, bitwidth, group_size)
@@ -174,23 +208,11 @@ def _matmul_impl(input: torch.Tensor, matgptq_weights: torch.Tensor, matgptq_sca
         raise RuntimeError(f"input and matgptq_scales must be {dtype} for feature_flag={feature_flag}")
     dev = matgptq_weights.device
     batch = input.size(-2)
-    x = input
-    if input.dim() > 2:
-        # the reference reads the last two dimensions only (csrc/bindings.cpp:171)
-        x = input.reshape(-1, batch, n_in_features)[0]
-    if not x.is_contiguous():
-        x = x.contiguous()
-    if x.data_ptr() % 16 != 0:
-        x = x.clone()
+    x = _prepare_input(input, batch, n_in_features)
     with torch.cuda.device(dev):
         out = torch.empty((batch, n_out_features), dtype=dtype, device=dev)
-        ws_bytes = _lib.matgptq_b200_matmul_workspace_bytes(n_out_features, n_in_features, batch)
-        ws = torch.empty(ws_bytes, dtype=torch.uint8, device=dev) if ws_bytes > 0 else None
-        st = _lib.matgptq_b200_matmul_ws(bitwidth, group_size, n_out_features, n_in_features, batch,
-                                         matgptq_weights.data_ptr(), matgptq_scales.data_ptr(), x.data_ptr(),
-                                         out.data_ptr(), _stream_ptr(dev), feature_flag,
-                                         ws.data_ptr() if ws is not None else None, ws_bytes, 0, 0)
-        _native.check(st, "matmul_matgptq")
+        _launch_matmul("matmul_matgptq", dev, bitwidth, group_size, n_out_features, n_in_features, batch,
+                       matgptq_weights, matgptq_scales, x, out, feature_flag)
     return out
 
 
@@ -219,6 +241,37 @@ def _matmul_fake(input, matgptq_weights, matgptq_scales, n_out_features, n_in_fe
                            dtype=torch.bfloat16 if feature_flag & 2 else torch.float16)
 
 
+@torch.library.custom_op("matgptq_cuda::matmul_matgptq_out", mutates_args=("out",))
+def matmul_matgptq_out(
+    input: torch.Tensor,
+    matgptq_weights: torch.Tensor,
+    matgptq_scales: torch.Tensor,
+    n_out_features: int,
+    n_in_features: int,
+    bitwidth: int,
+    group_size: int,
+    feature_flag: int,
+    out: torch.Tensor,
+) -> None:
+    """``matmul_matgptq`` into a tensor the caller owns (``out [M, N]``, contiguous, float16 or bfloat16 like the
+    input): nothing is allocated, which is what callers that gather several layers' outputs in one buffer, or that
+    capture the call in a CUDA graph with their own memory plan, want.  The reference's operator only has the
+    allocating form (csrc/bindings.cpp:158-201)."""
+    _check_matmul_args(input, matgptq_weights, matgptq_scales, n_out_features, n_in_features, bitwidth, group_size)
+    dtype = torch.bfloat16 if feature_flag & _native.FLAG_BF16 else torch.float16
+    if input.dtype != dtype or matgptq_scales.dtype != dtype:
+        raise RuntimeError(f"input and matgptq_scales must be {dtype} for feature_flag={feature_flag}")
+    batch = input.size(-2)
+    dev = matgptq_weights.device
+    if (out.dtype != dtype or out.device != dev or tuple(out.shape) != (batch, n_out_features) or not out.is_contiguous()
+            or out.data_ptr() % 2 != 0):
+        raise RuntimeError(f"out must be a contiguous {dtype} tensor of shape ({batch}, {n_out_features}) on {dev}")
+    x = _prepare_input(input, batch, n_in_features)
+    with torch.cuda.device(dev):
+        _launch_matmul("matmul_matgptq_out", dev, bitwidth, group_size, n_out_features, n_in_features, batch,
+                       matgptq_weights, matgptq_scales, x, out, feature_flag)
+
+
 def matmul_matgptq_grouped_raw(x: torch.Tensor, packed, scales, n_out, n_in: int, bitwidths, group_size: int,
                                flags: int, out: torch.Tensor | None = None,
                                workspace: torch.Tensor | None = None) -> torch.Tensor:
@@ -232,7 +285,7 @@ def matmul_matgptq_grouped_raw(x: torch.Tensor, packed, scales, n_out, n_in: int
     need = 0
     for i, (w, s, n, b) in enumerate(zip(packed, scales, n_out, bitwidths)):
         segs[i] = _native.Segment(w.data_ptr(), s.data_ptr(), int(n), int(b))
-        if batch >= 32 and workspace is None:
+        if batch >= 32 and workspace is None and flags & _native.FLAG_SCRATCH_REDUCE:
             need = max(need, _lib.matgptq_b200_matmul_workspace_bytes(int(n), n_in, batch))
     if need > 0:
         workspace = torch.empty(need, dtype=torch.uint8, device=x.device)
@@ -387,7 +440,7 @@ def matmul_matgptq_raw(x: torch.Tensor, packed: torch.Tensor, scales: torch.Tens
                                             scales.data_ptr(), x.data_ptr(), out.data_ptr(), stream, flags,
                                             warps_per_cta, split_k)
     else:
-        if workspace is None and path != 1:
+        if workspace is None and path != 1 and flags & _native.FLAG_SCRATCH_REDUCE:  # scratch only where it is used
             if path == 2 and split_k > 1:
                 need = split_k * batch * n_out * 4
             elif path == 2:

@@ -194,6 +194,28 @@ def test_input_views_and_errors(cuda):
     assert empty.shape == (0, n_out)
 
 
+@pytest.mark.parametrize("m", [1, 16, 48])
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_out_form_writes_the_callers_tensor(cuda, m, dtype):
+    """matmul_matgptq_out: the same bits as the allocating operator, written into a slice of a larger buffer (GEMV
+    and tensor-core path), nothing around the slice touched; a wrong `out` is an error."""
+    from matgptq_b200 import ops  # noqa: F401
+    n_out, n_in, b = 384, 1024, 3
+    packed, scales_r, w_ref, flag = _layer_and_ref(n_out, n_in, 128, b, dtype, 5, cuda)
+    x = synth.make_activations(m, n_in, seed=m, dtype=dtype, device=cuda)
+    y = torch.ops.matgptq_cuda.matmul_matgptq(x, packed, scales_r, n_out, n_in, b, 128, flag)
+    buf = torch.full((3 * m * n_out,), 7.0, dtype=dtype, device=cuda)
+    out = buf[m * n_out:2 * m * n_out].view(m, n_out)
+    assert torch.ops.matgptq_cuda.matmul_matgptq_out(x, packed, scales_r, n_out, n_in, b, 128, flag, out) is None
+    assert torch.equal(out, y)
+    assert (buf[:m * n_out] == 7.0).all() and (buf[2 * m * n_out:] == 7.0).all()
+    assert oracle.rel_err(out.cpu(), oracle.linear_fp32_accumulate(x.cpu(), w_ref)) <= TOL
+    with pytest.raises(RuntimeError, match="out must be"):
+        torch.ops.matgptq_cuda.matmul_matgptq_out(x, packed, scales_r, n_out, n_in, b, 128, flag, out[:, :-1])
+    with pytest.raises(RuntimeError, match="out must be"):
+        torch.ops.matgptq_cuda.matmul_matgptq_out(x, packed, scales_r, n_out, n_in, b, 128, flag, out.float())
+
+
 # ---- extension: per-group zero points (asymmetric quantisation) ---------------------------------------------
 
 def _asym_layer_and_ref(n_out, n_in, gs, b, dtype, seed, cuda):
