@@ -1,20 +1,20 @@
-// Tensor-core path for batches of 32 rows and more: tcgen05.mma with the accumulator
+// Tensor-core path for batches of more than 16 rows: tcgen05.mma with the accumulator
 // in tensor memory.
 //
 // Replaces gptq_matryoshka for large batches (csrc/matgptq_gemm.cu:337-634), which
 // re-reads the weights once per 8 batch columns and stays below a dense fp16 GEMM
 // from M = 32 up.  Here one CTA owns 128 out-features and up to 256 batch rows:
 //
-//   * eight "dequant" warps (one per 16-row tile of the packed layout) decode their
-//     block to the exact dense weights of the reference's dequantize()
-//     (round(scale * (code*2^(8-b) - 128)), fp16 or bf16) and store them K-major into a
-//     shared-memory stage in the canonical no-swizzle UMMA layout (8 x 16-byte core
-//     matrices), with the packed words of the next two or three blocks already in flight;
+//   * "dequant" warps (one per 16-row tile of the packed layout; two per tile, one 64-wide half each, when the
+//     CTA has its SM to itself) decode their block to the exact dense weights of the reference's dequantize()
+//     (round(scale * (code*2^(8-b) - 128)), fp16 or bf16) and store them K-major into a shared-memory stage
+//     in the canonical no-swizzle UMMA layout (8 x 16-byte core matrices), with the packed words of the next
+//     three to six blocks already in flight;
 //   * one thread of the last warp fetches the activation tiles (batch rows x 64 in-features) with TMA
 //     (cp.async.bulk.tensor.2d, 128-byte swizzle, rows past the batch filled with zeros), as far ahead as
-//     the pipeline has stages; an elected lane of the warp before it issues tcgen05.mma (M = 128 weight rows, N = batch rows, K = 16)
-//     from shared-memory descriptors; D[128, N] lives in tensor memory; completion of a stage's MMAs
-//     releases the stage through tcgen05.commit -> mbarrier;
+//     the pipeline has stages; an elected lane of the warp before it issues tcgen05.mma (M = 128 weight
+//     rows, N = batch rows, K = 16) from shared-memory descriptors; D[128, N] lives in tensor memory;
+//     completion of a stage's MMAs releases the stage through tcgen05.commit -> mbarrier;
 //   * the epilogue reads D with tcgen05.ld (each warp its own 32 TMEM lanes), converts
 //     and stores y[m, n] (the transpose of D); when K is split, the CTAs that share a tile form a
 //     thread-block cluster, leave their fp32 sums in shared memory, and each adds and stores a share
@@ -269,7 +269,7 @@ __device__ __forceinline__ void gemm_tc_body(const GemmParams &p, const CUtensor
   if (warp == PW) {
     if (lane == 0) {
       for (int i = 0; i < stages; ++i) {
-        mbar_init(bar_full + i * 8, 9);  // the eight producer warps and the thread that requests the activations
+        mbar_init(bar_full + i * 8, 9);  // the eight producer warps of a stage and the thread that requests the activations
         mbar_init(bar_empty + i * 8, 1);
       }
       mbar_init(bar_done, 1);
@@ -297,7 +297,7 @@ __device__ __forceinline__ void gemm_tc_body(const GemmParams &p, const CUtensor
     const bool valid = tile16 < p.N / 16;
     constexpr int BW = BlockTraits<B>::WORDS;
     constexpr int NG = TcScales<GS>::NG;
-    // Packed words and scales of two or three blocks in flight, in statically indexed registers: the block
+    // Packed words and scales of three to six blocks in flight, in statically indexed registers: the block
     // loop is unrolled so that no register is copied while its load is still outstanding.  Everything
     // inside the loop is a per-lane base plus a running offset: no multiplications, divisions or
     // modulo by the (runtime) number of stages.
@@ -532,9 +532,8 @@ static int round_up16(int v) { return (v + 15) / 16 * 16; }
 
 // Up to 128 batch rows the kernel is bound by its producer warps (eight per CTA), so two CTAs share an SM
 // whenever three pipeline stages of each fit in half of the SM's shared memory.  Measured on B200: two stages
-// are too shallow (256 batch rows: 45 us with one CTA and four stages, 53 us with two CTAs and two stages),
-// and at 256 rows sixteen producer warps in one CTA change nothing (the tensor pipe of the 112 to 128 SMs
-// that have a tile is then the limit).
+// are too shallow (256 batch rows: 45 us with one CTA and four stages, 53 us with two CTAs and two stages); a
+// CTA that has the SM to itself runs sixteen producer warps instead (gate/up at 256 rows: 37.9 -> 35.3 us).
 constexpr int kTcHalfSmBytes = 112 * 1024;
 static bool tc_two_ctas_per_sm(int ncols) { return tc_plan(ncols, 3).total <= kTcHalfSmBytes; }
 
