@@ -106,9 +106,10 @@ int matgptq_b200_matmul_ws(int64_t bitwidth, int64_t group_size, int64_t n_out, 
  * group size); segment i fills the columns [sum_{j<i} N_j, +N_i) of y.  This is the fused qkv / gate_up layer
  * of a model whose checkpoint layers carry different bitwidths (vLLM fuses them into one layer,
  * inference_lib/vllm_matgptq.py:113-121; the bitwidth file of evo_quant_search.py:659-671 gives each its own b).
- * Batches below 32 run as ONE kernel launch (every CTA looks its segment up in a table); larger batches run the
- * tensor-core path once per segment into the column block of that segment (workspace as for
- * matgptq_b200_matmul_ws, sized for the largest segment; may be NULL).  Up to 8 segments.  The reference has no
+ * Batches of up to 16 rows run as ONE kernel launch (every CTA looks its segment up in a table); larger batches
+ * run one launch per segment into the column block of that segment, each the way matgptq_b200_matmul would run
+ * it (the tensor-core path from 17 or 25 rows; workspace as for matgptq_b200_matmul_ws, sized for the largest
+ * segment; may be NULL).  Up to 8 segments.  The reference has no
  * counterpart: its operator takes one bitwidth per call.
  */
 typedef struct {

@@ -45,8 +45,8 @@ const char *matgptq_b200_strerror(int status) {
   }
 }
 
-// Batches from this size on always take the tensor-core path (tcgen05); the fused and grouped small-batch
-// entry points serve batches below it.
+// The row-parallel product with the fused all-reduce serves batches below this size (two passes of the GEMV from 17
+// rows on); larger batches take the tensor-core path and a library all-reduce.
 static const int64_t kTensorCoreMinBatch = 32;
 
 // Automatic choice between the GEMV family and the tensor-core path.  The GEMV handles 16 activation rows per
@@ -154,18 +154,19 @@ int matgptq_b200_matmul_grouped(const matgptq_b200_segment *segments, int n_segm
   for (int i = 0; i < n_segments; ++i)
     segs[i] = mg::GroupedSegment{segments[i].w, segments[i].s, static_cast<int>(segments[i].n_out),
                                  static_cast<int>(segments[i].bitwidth)};
-  if (batch < kTensorCoreMinBatch) {
+  if (batch <= 16) {  // one pass of the GEMV: all segments in one launch
     r = mg::gemv_grouped_launch(segs, n_segments, static_cast<int>(group_size), static_cast<int>(n_in),
                                 static_cast<int>(batch), x, y, static_cast<int>(total), bf16, pdl, cs);
   }
   if (r == MG_ERR_UNSUPPORTED) {
-    // One launch per segment into its column block: segments that cannot share a launch shape, and the tensor-core
-    // path (a grouped launch of it was measured: level with launches that overlap through programmatic dependent
+    // One launch per segment into its column block: segments that cannot share a launch shape, and batches of more
+    // than 16 rows, where each segment goes the way matgptq_b200_matmul would send it (a grouped launch of the
+    // tensor-core path was measured: level with launches that overlap through programmatic dependent
     // launch up to 64 rows and at 256, 5 % ahead at 128 for gate and up of Llama-3.1-8B; not kept).
     int64_t col = 0;
     for (int i = 0; i < n_segments; ++i) {
       unsigned char *yi = static_cast<unsigned char *>(y) + col * 2;
-      if (batch >= kTensorCoreMinBatch)
+      if (uses_tensor_cores(segments[i].n_out, batch))
         r = mg::gemm_tc_launch(static_cast<int>(segments[i].bitwidth), static_cast<int>(group_size),
                                static_cast<int>(segments[i].n_out), static_cast<int>(n_in), static_cast<int>(batch),
                                segments[i].w, segments[i].s, x, yi, workspace, workspace_bytes, bf16, pdl, 0, cs,

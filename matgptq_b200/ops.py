@@ -276,7 +276,7 @@ def matmul_matgptq_grouped_raw(x: torch.Tensor, packed, scales, n_out, n_in: int
                                flags: int, out: torch.Tensor | None = None,
                                workspace: torch.Tensor | None = None) -> torch.Tensor:
     """The C-ABI grouped product without checks: segment ``i`` (``packed[i]``, ``scales[i]``, ``n_out[i]`` rows at
-    ``bitwidths[i]`` bits) fills its column block of ``out [M, sum(n_out)]``.  One kernel launch below 32 rows."""
+    ``bitwidths[i]`` bits) fills its column block of ``out [M, sum(n_out)]``.  One kernel launch up to 16 rows."""
     batch = x.size(-2)
     total = int(sum(n_out))
     if out is None:
@@ -310,7 +310,7 @@ def matmul_matgptq_grouped(
 ) -> torch.Tensor:
     """Addition: ``matmul_matgptq`` for a fused layer whose output partitions have their own bitwidths
     (``vllm_matgptq.py:113-121`` fuses q/k/v and gate/up; ``evo_quant_search.py:659-671`` gives each checkpoint
-    layer its own bitwidth).  ``y[M, sum N_i] = x[M, K] @ cat(Wdq_i).T`` in one launch for fewer than 32 rows;
+    layer its own bitwidth).  ``y[M, sum N_i] = x[M, K] @ cat(Wdq_i).T`` in one launch up to 16 rows;
     the reference's operator takes a single bitwidth per call."""
     if not (len(matgptq_weights) == len(matgptq_scales) == len(n_out_features) == len(bitwidths)) or not matgptq_weights:
         raise RuntimeError("matmul_matgptq_grouped: one weight, scale, n_out_features and bitwidth per segment")
