@@ -58,6 +58,11 @@ class MatGPTQConfig(QuantizationConfig):
         self.layer_bitwidths = dict(layer_bitwidths) if layer_bitwidths else None
         self.zero_points = bool(zero_points)
         self.flag = MatGTPQ_FeatureFlags.ASYNC + MatGTPQ_FeatureFlags.IS_BF16 * (self.quant_dtype == torch.bfloat16)
+        # what the products are launched with: programmatic dependent launch on top, so that launches of this library
+        # that follow one another (the segments of a fused layer above 16 rows) prefetch weights behind each other;
+        # behind a kernel of the host that does not release its dependents early the launch simply starts when that
+        # kernel is done, as it would without the flag
+        self.matmul_flag = int(self.flag) | 4
 
     def get_name(self) -> str:
         return "matgptq_quant"
@@ -178,19 +183,19 @@ class MatGPTQLinearMethod(LinearMethodBase):
         if cfg.zero_points:
             outs = [
                 torch.ops.matgptq_cuda.matmul_matgptq_zeros(x2, w, s, z, rows, layer.matgptq_n_in, bits, cfg.group_size,
-                                                            cfg.flag)
+                                                            cfg.matmul_flag)
                 for (rows, bits), w, s, z in zip(layer.matgptq_segments, layer.matgptq_weights, layer.matgptq_scales,
                                                  layer.matgptq_zeros)
             ]
         elif len(layer.matgptq_segments) == 1:
             (rows, bits), = layer.matgptq_segments
             outs = [torch.ops.matgptq_cuda.matmul_matgptq(x2, layer.matgptq_weights[0], layer.matgptq_scales[0], rows,
-                                                          layer.matgptq_n_in, bits, cfg.group_size, cfg.flag)]
+                                                          layer.matgptq_n_in, bits, cfg.group_size, cfg.matmul_flag)]
         else:
             # a fused layer whose partitions carry different bitwidths: one grouped launch, outputs side by side
             outs = [torch.ops.matgptq_cuda.matmul_matgptq_grouped(
                 x2, list(layer.matgptq_weights), list(layer.matgptq_scales), [rows for rows, _ in layer.matgptq_segments],
-                layer.matgptq_n_in, [bits for _, bits in layer.matgptq_segments], cfg.group_size, cfg.flag)]
+                layer.matgptq_n_in, [bits for _, bits in layer.matgptq_segments], cfg.group_size, cfg.matmul_flag)]
         y = outs[0] if len(outs) == 1 else torch.cat(outs, dim=-1)
         y = y.view(*x.shape[:-1], y.shape[-1])
         if bias is not None:
