@@ -14,6 +14,11 @@ class MatGTPQ_FeatureFlags(IntEnum):
     PDL = 4
 
 
+# forward() launches with programmatic dependent launch on top of the module's flag (the reference's two bits):
+# q, k, v or gate, up of a model that calls one module after the other then prefetch their weights behind each other
+_PDL = int(MatGTPQ_FeatureFlags.PDL)
+
+
 class MatGPTQLinear(torch.nn.Module):
     """Linear layer over packed b-bit weights.
 
@@ -89,8 +94,8 @@ class MatGPTQLinear(torch.nn.Module):
             # beyond.  Here every leading dimension counts as rows and the result keeps them.
             y = torch.ops.matgptq_cuda.matmul_matgptq(
                 x.reshape(-1, self.n_in_features), self.matgptq_qweight, self.matgptq_scales, self.n_out_features,
-                self.n_in_features, self.bitwidth, self.group_size, self.flag)
+                self.n_in_features, self.bitwidth, self.group_size, self.flag | _PDL)
             return y.view(*x.shape[:-1], self.n_out_features)
         return torch.ops.matgptq_cuda.matmul_matgptq(
             x, self.matgptq_qweight, self.matgptq_scales, self.n_out_features, self.n_in_features,
-            self.bitwidth, self.group_size, self.flag)
+            self.bitwidth, self.group_size, self.flag | _PDL)
